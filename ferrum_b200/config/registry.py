@@ -89,3 +89,5 @@ def _ensure_builtin():
         from ..models import ruperax  # noqa: F401
     if "Vikupel" not in _REGISTRY:
         from ..models import vikupel  # noqa: F401
+    if "Zavesun" not in _REGISTRY:
+        from ..models import zavesun  # noqa: F401

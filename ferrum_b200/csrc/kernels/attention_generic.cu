@@ -21,7 +21,9 @@
 // absolute key positions: a function of the position alone, never of the batch.
 // Formulas: query head h reads KV head h / (Hq/Hkv), score = q.k / sqrt(D), stable softmax,
 // weighted sum of V (crates/model/src/llama.rs:220-247; crates/kernels/src/scalar.rs:125-141).
-// `window` > 0 keeps keys in (pos-window, pos].
+// `window` > 0 keeps keys in (pos-window, pos]; with `chunked` the same number is the length of a
+// chunk instead: positions are cut into chunks of `window` from position 0 and a query sees the
+// keys of its own chunk up to itself.
 #include "common.cuh"
 
 constexpr int AG_WARPS = 4;
@@ -89,10 +91,17 @@ __device__ __forceinline__ void ag_store(T* out, size_t idx, float v, int out_f3
   else out[idx] = from_f32<T>(v);
 }
 
-// A penalty on distance, taken off the scaled score: bias1[h] * ln(1 + bias2[h] * (pos - key)); no
-// penalty when bias1 is null.
+// A penalty on distance, taken off the scaled score: bias1[h] * ln(1 + bias2[h] * (pos - key)), or the
+// straight line bias1[h] * (pos - key) when bias2 is null; no penalty when bias1 is null.
 __device__ __forceinline__ float ag_distance_penalty(const float* bias1, const float* bias2, int h, int dist) {
-  return bias1 == nullptr ? 0.f : bias1[h] * log1pf(bias2[h] * (float)dist);
+  if (bias1 == nullptr) return 0.f;
+  return bias2 == nullptr ? bias1[h] * (float)dist : bias1[h] * log1pf(bias2[h] * (float)dist);
+}
+
+// The first key a query at `pos` sees: a sliding window of `window` keys, or (chunked) the start of its chunk.
+__device__ __forceinline__ int ag_first_key(int pos, int window, int chunked) {
+  if (window <= 0) return 0;
+  return chunked ? (pos / window) * window : max(0, pos - window + 1);
 }
 
 // part: null (the CTA covers the row's whole key range and writes `out`), or the partials
@@ -107,7 +116,7 @@ attention_generic_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, 
                          const int* __restrict__ block_table, int table_width, const T* __restrict__ kv_plane,
                          long long page_stride, int page_size, int Hq, int Hkv, int D, float scale, int window,
                          int* __restrict__ err, float* __restrict__ part, int split_slots, int vec,
-                         const float* __restrict__ bias1, const float* __restrict__ bias2, int out_f32) {
+                         const float* __restrict__ bias1, const float* __restrict__ bias2, int out_f32, int chunked) {
   using Tile = AgTile<DI>;
   constexpr int TK = Tile::TK, DP = Tile::DP, KS = Tile::KS;
   extern __shared__ __align__(16) float ag_smem[];
@@ -125,7 +134,7 @@ attention_generic_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, 
   const int h0 = kvh * G + chunk * AG_HEADS;
   const int nh = min(AG_HEADS, G - chunk * AG_HEADS);
   const int pos = positions[t];
-  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int lo = ag_first_key(pos, window, chunked);
   int k_begin = lo, k_end = pos + 1;
   if (part != nullptr) {
     const int s = lo / AG_SPLIT + blockIdx.y;
@@ -356,7 +365,7 @@ attention_generic_tokens_kernel(const T* __restrict__ q, int ldq, T* __restrict_
                                 const int* __restrict__ block_table, int table_width, const T* __restrict__ kv_plane,
                                 long long page_stride, int page_size, int Hq, int Hkv, int D, float scale, int window,
                                 int* __restrict__ err, int vec, const float* __restrict__ bias1,
-                                const float* __restrict__ bias2, int out_f32) {
+                                const float* __restrict__ bias2, int out_f32, int chunked) {
   using Tile = AgTile<DI>;
   using TT = AgTokenTile<DI>;
   constexpr int TK = Tile::TK, DP = Tile::DP, KS = Tile::KS;
@@ -401,7 +410,7 @@ attention_generic_tokens_kernel(const T* __restrict__ q, int ldq, T* __restrict_
   for (int i = 0; i < AG_TQ; ++i) {
     if (i < nt) {
       const int p = positions[t0 + i];
-      k_begin = min(k_begin, window > 0 ? max(0, p - window + 1) : 0);
+      k_begin = min(k_begin, ag_first_key(p, window, chunked));
       k_end = max(k_end, p + 1);
     }
   }
@@ -409,7 +418,7 @@ attention_generic_tokens_kernel(const T* __restrict__ q, int ldq, T* __restrict_
 #pragma unroll
   for (int i = 0; i < AG_TH; ++i) {
     pos[i] = i0 + i < nt ? positions[t0 + i0 + i] : -1;
-    lo[i] = i0 + i < nt ? (window > 0 ? max(0, pos[i] - window + 1) : 0) : 0x7fffffff;
+    lo[i] = i0 + i < nt ? ag_first_key(pos[i], window, chunked) : 0x7fffffff;
   }
   const int* bt = block_table + (size_t)req * table_width;
   const size_t v_off = (size_t)Hkv * page_size * D;
@@ -572,10 +581,10 @@ attention_generic_tokens_kernel(const T* __restrict__ q, int ldq, T* __restrict_
 template <typename T>
 __global__ void __launch_bounds__(32)
 attention_generic_combine_kernel(T* __restrict__ out, int ldo, const float* __restrict__ part, const int* __restrict__ positions,
-                                 int Hq, int D, int window, int split_slots, int out_f32) {
+                                 int Hq, int D, int window, int split_slots, int out_f32, int chunked) {
   const int t = blockIdx.x, h = blockIdx.y, lane = threadIdx.x;
   const int pos = positions[t];
-  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int lo = ag_first_key(pos, window, chunked);
   const int n = pos / AG_SPLIT - lo / AG_SPLIT + 1;
   const float* base = part + ((size_t)t * Hq + h) * split_slots * (D + 2);
   float M = -INFINITY, L = 0.f, O[AG_DI];
@@ -624,7 +633,7 @@ FERRUM_API int ferrum_attention_generic_split() { return AG_SPLIT; }
 // cut at multiples of 128 keys among split_slots CTAs (split_slots must cover the longest row),
 // and a second launch folds the partials into `out`.
 // bias1, bias2 (float32 per query head on the device, or null): the distance penalty above.  out_f32: the
-// output rows are float32 whatever the cache's type.
+// output rows are float32 whatever the cache's type.  chunked: `window` is a chunk length (see the top).
 // q_start (n_reqs + 1 entries on the device; may be null): with it and without `part`, tokens of a
 // request that follow each other in the batch share their key tiles (the kernel for prompt portions).
 FERRUM_API int ferrum_attention_generic(const void* q, int ldq, void* out, int ldo, int dtype, int n_tokens,
@@ -632,7 +641,7 @@ FERRUM_API int ferrum_attention_generic(const void* q, int ldq, void* out, int l
                                         int table_width, const void* kv_plane, long long page_stride, int page_size,
                                         int Hq, int Hkv, int D, float scale, int window, int* err_flag, float* part,
                                         int split_slots, const int* q_start, int n_reqs, const float* bias1,
-                                        const float* bias2, int out_f32, cudaStream_t stream) {
+                                        const float* bias2, int out_f32, int chunked, cudaStream_t stream) {
   FERRUM_CHECK_ARG(n_tokens >= 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0, "attention: bad head counts Hq=%d Hkv=%d", Hq, Hkv);
   FERRUM_CHECK_ARG(D > 0 && D <= AG_MAX_D, "attention: head size %d is outside (0, %d]", D, AG_MAX_D);
   FERRUM_CHECK_ARG(page_size > 0 && table_width > 0 && window >= 0, "attention: bad cache arguments");
@@ -661,7 +670,7 @@ FERRUM_API int ferrum_attention_generic(const void* q, int ldq, void* out, int l
     }                                                                                                                   \
     attention_generic_tokens_kernel<T, DI_><<<(unsigned)ctas, AG_TWARPS * 32, AgTokenTile<DI_>::SMEM_BYTES, stream>>>(   \
       (const T*)q, ldq, (T*)out, ldo, positions, q_start, n_reqs, block_table, table_width, (const T*)kv_plane,         \
-      page_stride, page_size, Hq, Hkv, D, scale, window, err_flag, vec, bias1, bias2, out_f32);                                             \
+      page_stride, page_size, Hq, Hkv, D, scale, window, err_flag, vec, bias1, bias2, out_f32, chunked);                                          \
   })
     if (D <= 32) AG_LAUNCH_TOKENS(1);
     else if (D <= 64) AG_LAUNCH_TOKENS(2);
@@ -684,7 +693,7 @@ FERRUM_API int ferrum_attention_generic(const void* q, int ldq, void* out, int l
     }                                                                                                                   \
     attention_generic_kernel<T, DI_><<<grid, AG_WARPS * 32, AgTile<DI_>::SMEM_BYTES, stream>>>(                        \
       (const T*)q, ldq, (T*)out, ldo, positions, req_of_token, block_table, table_width, (const T*)kv_plane, page_stride, \
-      page_size, Hq, Hkv, D, scale, window, err_flag, part, split_slots, vec, bias1, bias2, out_f32);                                       \
+      page_size, Hq, Hkv, D, scale, window, err_flag, part, split_slots, vec, bias1, bias2, out_f32, chunked);                                    \
   })
   if (D <= 32) AG_LAUNCH(1);
   else if (D <= 64) AG_LAUNCH(2);
@@ -696,7 +705,7 @@ FERRUM_API int ferrum_attention_generic(const void* q, int ldq, void* out, int l
     const dim3 cgrid(n_tokens, Hq);
     FERRUM_CHECK_ARG(cgrid.y <= 65535, "attention: too many heads");
     FERRUM_DISPATCH_DTYPE(dtype, T, (attention_generic_combine_kernel<T><<<cgrid, 32, 0, stream>>>(
-        (T*)out, ldo, part, positions, Hq, D, window, split_slots, out_f32)));
+        (T*)out, ldo, part, positions, Hq, D, window, split_slots, out_f32, chunked)));
     FERRUM_CHECK_LAUNCH("attention_generic_combine");
   }
   return 0;

@@ -1,12 +1,17 @@
 // What surrounds the attention kernel for mixers whose heads are shaped before and after it:
 //
 // qkv_shape: reads one float32 row per token [q heads | k heads | v heads | ...] as a product left
-// it, and per head, in float32: turns the leading `rope_dim` elements of a query or key head by the
-// token's position (table of cos/sin per position and pair; pairs (i, i + rope_dim/2) or (2i, 2i+1)),
-// then, when asked, divides the whole head by its root mean square (no weight); turns a value head
-// over all of its elements by a table of its own.  Queries go out in the compute type [T, Hq, Dp],
-// keys and values go to the token's place in the paged cache (rows of Dp elements, zero past the
-// head's own size: Dp = max(key size, value size) lets one page layout hold both).
+// it, and per head, in float32, in this order: adds the projection's bias; divides a query or key head
+// by its root mean square and multiplies by a weight vector shared by all heads (`qnorm_w`, `knorm_w`);
+// turns the leading `rope_dim` elements of a query or key head by the token's position (table of
+// cos/sin per position and pair; pairs (i, i + rope_dim/2) or (2i, 2i+1)); then, when asked, divides
+// the whole head by its root mean square (no weight); multiplies a query head by a temperature of its
+// position, 1 + coef * ln(floor((pos + 1) / every) + 1); turns a value head over all of its elements
+// by a table of its own; blends a value head with the same token's value head of an earlier layer,
+// (1 - lambda) v + lambda v_first (`vmix_mode` 2), or leaves its own there for later layers (1).
+// Queries go out in the compute type [T, Hq, Dp], keys and values go to the token's place in the
+// paged cache (rows of Dp elements, zero past the head's own size: Dp = max(key size, value size)
+// lets one page layout hold both).
 //
 // attention_finish: reads the attention's float32 output [T, Hq, Dp]; turns each head back by the
 // query's position (the inverse of the value rotation), multiplies by a sigmoid gate whose logits lie
@@ -18,6 +23,19 @@
 constexpr int AP_WARPS = 4;
 constexpr int AP_MAX_D = 256;
 
+// What a head may need beyond rotation and unit norm; every pointer may be null.
+struct HeadExtras {
+  const float* bias;        // [Hq*Dk + Hkv*Dk + Hkv*Dv], laid out like the product's row
+  const float* qnorm_w;     // [Dk]
+  const float* knorm_w;     // [Dk]
+  float qtemp_coef;
+  int qtemp_every;          // 0: no temperature
+  int vmix_mode;            // 0: none; 1: leave this layer's values in v_first; 2: blend with v_first
+  float* v_first;           // [T, ld_first] float32
+  int ld_first;
+  const float* v_lambda;    // one float on the device
+};
+
 template <typename T>
 __global__ void __launch_bounds__(AP_WARPS * 32)
 qkv_shape_kernel(const float* __restrict__ proj, int ldp, int n_tokens, const int* __restrict__ positions,
@@ -25,7 +43,7 @@ qkv_shape_kernel(const float* __restrict__ proj, int ldp, int n_tokens, const in
                  const float* __restrict__ cs_qk, int rope_dim, int qk_pairing, int n_pos_qk,
                  const float* __restrict__ cs_v, int v_pairing, int n_pos_v, int unit_norm, float eps,
                  T* __restrict__ q_out, int ldq, T* __restrict__ plane, long long page_stride, int page_size,
-                 int Hq, int Hkv, int Dk, int Dv, int Dp, int writes, int* __restrict__ err) {
+                 int Hq, int Hkv, int Dk, int Dv, int Dp, int writes, int* __restrict__ err, const HeadExtras x) {
   __shared__ float rows[AP_WARPS][AP_MAX_D];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int slots = Hq + (writes ? 2 * Hkv : 0);
@@ -38,8 +56,21 @@ qkv_shape_kernel(const float* __restrict__ proj, int ldp, int n_tokens, const in
   const int D = is_v ? Dv : Dk;
   const int src_off = slot < Hq ? slot * Dk : (slot < Hq + Hkv ? Hq * Dk + (slot - Hq) * Dk : (Hq + Hkv) * Dk + (slot - Hq - Hkv) * Dv);
   const float* src = proj + (size_t)t * ldp + src_off;
-  for (int d = lane; d < D; d += 32) row[d] = src[d];
+  if (x.bias != nullptr) {
+    for (int d = lane; d < D; d += 32) row[d] = src[d] + x.bias[src_off + d];
+  } else {
+    for (int d = lane; d < D; d += 32) row[d] = src[d];
+  }
   __syncwarp();
+  const float* nw = is_v ? nullptr : (slot < Hq ? x.qnorm_w : x.knorm_w);
+  if (nw != nullptr) {                       // weighted RMS norm of the head, before any turn
+    float ss = 0.f;
+    for (int d = lane; d < D; d += 32) ss = fmaf(row[d], row[d], ss);
+    ss = warp_sum(ss);
+    const float r = 1.f / sqrtf(ss / (float)D + eps);
+    for (int d = lane; d < D; d += 32) row[d] = row[d] * r * nw[d];
+    __syncwarp();
+  }
   const float* cs = is_v ? cs_v : cs_qk;
   const int R = is_v ? Dv : rope_dim;
   const int pairing = is_v ? v_pairing : qk_pairing;
@@ -64,6 +95,17 @@ qkv_shape_kernel(const float* __restrict__ proj, int ldp, int n_tokens, const in
     for (int d = lane; d < D; d += 32) ss = fmaf(row[d], row[d], ss);
     ss = warp_sum(ss);
     mult = 1.f / sqrtf(ss / (float)D + eps);
+  }
+  if (slot < Hq && x.qtemp_every > 0) mult *= 1.f + x.qtemp_coef * logf((float)((pos + 1) / x.qtemp_every + 1));
+  if (is_v && x.vmix_mode != 0) {
+    float* first = x.v_first + (size_t)t * x.ld_first + (size_t)(slot - Hq - Hkv) * Dv;
+    if (x.vmix_mode == 1) {
+      for (int d = lane; d < D; d += 32) first[d] = row[d];
+    } else {
+      const float lam = *x.v_lambda;
+      for (int d = lane; d < D; d += 32) row[d] = (1.f - lam) * row[d] + lam * first[d];
+    }
+    __syncwarp();
   }
   T* dst;
   if (slot < Hq) {
@@ -126,20 +168,26 @@ FERRUM_API int ferrum_qkv_shape(const float* proj, int ldp, int n_tokens, const 
                                 const int* block_table, int table_width, const float* cs_qk, int rope_dim, int qk_pairing,
                                 int n_pos_qk, const float* cs_v, int v_pairing, int n_pos_v, int unit_norm, float eps,
                                 void* q_out, int ldq, void* plane, long long page_stride, int page_size, int dtype, int Hq,
-                                int Hkv, int Dk, int Dv, int Dp, int writes, int* err, cudaStream_t stream) {
+                                int Hkv, int Dk, int Dv, int Dp, int writes, int* err, const float* bias,
+                                const float* qnorm_w, const float* knorm_w, float qtemp_coef, int qtemp_every,
+                                int vmix_mode, float* v_first, int ld_first, const float* v_lambda, cudaStream_t stream) {
   FERRUM_CHECK_ARG(Hq > 0 && Hkv > 0 && Dk > 0 && Dv > 0 && Dp >= Dk && Dp >= Dv && Dp <= AP_MAX_D,
                    "qkv_shape: bad head sizes Dk=%d Dv=%d Dp=%d", Dk, Dv, Dp);
   FERRUM_CHECK_ARG(rope_dim >= 0 && rope_dim <= Dk && rope_dim % 2 == 0, "qkv_shape: bad rotary size %d", rope_dim);
   FERRUM_CHECK_ARG(cs_v == nullptr || Dv % 2 == 0, "qkv_shape: a rotated value needs an even size");
   FERRUM_CHECK_ARG(page_size > 0 && table_width > 0, "qkv_shape: bad cache arguments");
+  FERRUM_CHECK_ARG(qtemp_every >= 0 && vmix_mode >= 0 && vmix_mode <= 2, "qkv_shape: bad temperature or value-mix arguments");
+  FERRUM_CHECK_ARG(vmix_mode == 0 || (v_first != nullptr && ld_first >= Hkv * Dv && (vmix_mode == 1 || v_lambda != nullptr)),
+                   "qkv_shape: value mixing needs the first layer's values and a blend factor");
   if (n_tokens == 0) return 0;
+  const HeadExtras extras{bias, qnorm_w, knorm_w, qtemp_coef, qtemp_every, vmix_mode, v_first, ld_first, v_lambda};
   const long long items = (long long)n_tokens * (Hq + (writes ? 2 * Hkv : 0));
   const long long blocks = (items + AP_WARPS - 1) / AP_WARPS;
   FERRUM_CHECK_ARG(blocks < (1LL << 31), "qkv_shape: too many rows");
   FERRUM_DISPATCH_DTYPE(dtype, T, (qkv_shape_kernel<T><<<(unsigned)blocks, AP_WARPS * 32, 0, stream>>>(
       proj, ldp, n_tokens, positions, req_of_token, block_table, table_width, cs_qk, rope_dim, qk_pairing, n_pos_qk, cs_v,
       v_pairing, n_pos_v, unit_norm, eps, (T*)q_out, ldq, (T*)plane, page_stride, page_size, Hq, Hkv, Dk, Dv, Dp, writes,
-      err)));
+      err, extras)));
   FERRUM_CHECK_LAUNCH("qkv_shape");
   return 0;
 }

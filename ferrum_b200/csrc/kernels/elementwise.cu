@@ -8,9 +8,11 @@
 // ---------------------------------------------------------------- embedding
 // out[t, :] = table[ids[t], :] as float32 (the residual stream is float32 in every mode).
 // An id outside [0, V) writes zeros and raises the error flag: never a wild read.
+// `copies` > 1: a token's row is written that many times in a row (a model that keeps several
+// copies of the residual stream starts them all from the embedded token).
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids,
-                                 float* __restrict__ out, int E, int V, int* __restrict__ err) {
+                                 float* __restrict__ out, int E, int V, int* __restrict__ err, int copies) {
   pdl_launch();
   pdl_wait();
   const int t = blockIdx.x;
@@ -18,16 +20,19 @@ __global__ void embedding_kernel(const T* __restrict__ table, const int* __restr
   const bool ok = id >= 0 && id < V;
   if (!ok && threadIdx.x == 0) atomicExch(err, 1);
   const T* row = table + (size_t)(ok ? id : 0) * E;
-  float* o = out + (size_t)t * E;
-  for (int i = threadIdx.x; i < E; i += blockDim.x) o[i] = ok ? to_f32<T>(row[i]) : 0.f;
+  float* o = out + (size_t)t * E * copies;
+  for (int i = threadIdx.x; i < E; i += blockDim.x) {
+    const float v = ok ? to_f32<T>(row[i]) : 0.f;
+    for (int c = 0; c < copies; ++c) o[(size_t)c * E + i] = v;
+  }
 }
 
 FERRUM_API int ferrum_embedding(const void* table, int dtype, const int* ids, float* out, int n_tokens,
-                                int E, int V, int* err_flag, cudaStream_t stream) {
-  FERRUM_CHECK_ARG(n_tokens >= 0 && E > 0 && V > 0, "embedding: bad sizes T=%d E=%d V=%d", n_tokens, E, V);
+                                int E, int V, int* err_flag, int copies, cudaStream_t stream) {
+  FERRUM_CHECK_ARG(n_tokens >= 0 && E > 0 && V > 0 && copies >= 1, "embedding: bad sizes T=%d E=%d V=%d", n_tokens, E, V);
   if (n_tokens == 0) return 0;
   const int threads = E >= 1024 ? 256 : 128;
-  FERRUM_DISPATCH_DTYPE(dtype, T, launch_kernel(embedding_kernel<T>, n_tokens, threads, 0, stream, (const T*)table, ids, out, E, V, err_flag));
+  FERRUM_DISPATCH_DTYPE(dtype, T, launch_kernel(embedding_kernel<T>, n_tokens, threads, 0, stream, (const T*)table, ids, out, E, V, err_flag, copies));
   FERRUM_CHECK_LAUNCH("embedding");
   return 0;
 }
@@ -713,3 +718,22 @@ FERRUM_API int ferrum_swiglu(const void* gu, void* act, int dtype, int n_tokens,
 }
 
 FERRUM_TRACE_READER(ferrum_trace_elementwise)
+
+// ---------------------------------------------------------------- soft cap of the logits
+// x <- cap * tanh(x / cap), in place, float32.
+__global__ void __launch_bounds__(256)
+softcap_kernel(float* __restrict__ x, int ld, int n, float cap, long long total) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  float* p = x + (size_t)(i / n) * ld + (i % n);
+  *p = cap * tanhf(*p / cap);
+}
+
+FERRUM_API int ferrum_softcap(float* x, int ld, int n_rows, int n, float cap, cudaStream_t stream) {
+  FERRUM_CHECK_ARG(n > 0 && ld >= n && cap > 0.f, "softcap: bad arguments");
+  if (n_rows == 0) return 0;
+  const long long total = (long long)n_rows * n;
+  softcap_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(x, ld, n, cap, total);
+  FERRUM_CHECK_LAUNCH("softcap");
+  return 0;
+}

@@ -157,6 +157,9 @@ class StepContext:
         # A residual product of a few tokens may stay in partials until the next norm adds it
         # (one kernel less on the critical path): (residual tensor, ops.Partials) or None.
         self.pending_residual = None
+        # A block that keeps several residual streams leaves its sublayer's write to the kernel that reads
+        # the streams next: (streams tensor, S, E, ops.StreamWrite) or None.
+        self.pending_streams = None
         self.defer_residuals = True
         self.defer_swiglu = True
         self.h2d_bytes = 0            # bytes copied to the device by the last fill
@@ -245,6 +248,7 @@ class StepContext:
         self.max_kv_len = max((p + n for p, n in zip(self.h_pos0, self.h_q_len)), default=0)
         self.step_cache = {}
         self.pending_residual = None
+        self.pending_streams = None
 
     def buffers_generation(self):
         """Changes whenever a buffer that kernels read may have moved (a captured graph is stale then)."""
@@ -265,12 +269,34 @@ class StepContext:
 
     def flush_residual(self):
         """Adds a pending residual product to its tensor (for consumers that do not know
-        about partials, and before the product workspace is used again)."""
+        about partials, and before the product workspace is used again); likewise a pending write
+        into several residual streams."""
         p = self.pending_residual
         if p is not None:
             from ..ops import lib as ops
             self.pending_residual = None
             ops.residual_reduce(p[0], self.n_tokens, p[1])
+        p = self.pending_streams
+        if p is not None:
+            from ..ops import lib as ops
+            self.pending_streams = None
+            ops.hyper_step(p[0], p[1], p[2], self.n_tokens, write=p[3], store=True)
+
+    def take_pending_streams(self, X):
+        """For a kernel about to read the streams `X`: the write it must apply first, or None."""
+        p = self.pending_streams
+        if p is None:
+            return None
+        if p[0].data_ptr() == X.data_ptr():
+            self.pending_streams = None
+            return p[3]
+        self.flush_residual()
+        return None
+
+    def drop_pending(self):
+        """Nobody reads the residual rows any more in this step."""
+        self.pending_residual = None
+        self.pending_streams = None
 
     # ------------------------------------------------------------------ scratch
     def buf(self, name, shape, dtype):

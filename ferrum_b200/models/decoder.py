@@ -96,7 +96,7 @@ class DecoderModel(Part):
             if NVTX:
                 torch.cuda.nvtx.range_pop()
         if ctx.n_want == 0:
-            ctx.pending_residual = None      # nobody reads the residual stream any more
+            ctx.drop_pending()               # nobody reads the residual stream any more
             return None
         x = self.final_norm.forward(h, ctx, rows=ctx.want_rows, n_rows=ctx.n_want, tag="final_norm")
         ctx.flush_residual()

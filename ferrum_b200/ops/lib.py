@@ -26,7 +26,7 @@ TC_STORE_BF16, TC_STORE_F32, TC_RESIDUAL, TC_SWIGLU = 0, 1, 2, 3       # tcgen05
 
 _lib = None
 _lock = threading.Lock()
-ABI = 12
+ABI = 13
 
 
 def lib():
@@ -205,15 +205,18 @@ def dtype_code(dtype):
 
 
 # ----------------------------------------------------------------------------- ops
-def embedding(table, ids, out, err, scale=1.0, pos_table=None, positions=None):
+def embedding(table, ids, out, err, scale=1.0, pos_table=None, positions=None, copies=1):
     """out[t] = table[ids[t]] as float32; with `scale` the row is multiplied by it, with `pos_table`
-    ([positions, E], the table's dtype) row positions[t] of it is added."""
+    ([positions, E], the table's dtype) row positions[t] of it is added.  copies > 1: out is
+    [>=T, copies * E] and receives the row that many times."""
     _need(table, None, "table", 2); _need(ids, torch.int32, "ids", 1); _need(out, torch.float32, "out", 2)
     V, E = table.shape
     T = ids.shape[0]
-    if out.shape[0] < T or out.shape[1] != E or not table.is_contiguous() or not out.is_contiguous():
-        raise KernelError("embedding: out must be contiguous [>=T, E] and table contiguous")
+    if out.shape[0] < T or out.shape[1] != E * copies or not table.is_contiguous() or not out.is_contiguous():
+        raise KernelError("embedding: out must be contiguous [>=T, copies * E] and table contiguous")
     if scale != 1.0 or pos_table is not None:
+        if copies != 1:
+            raise KernelError("embedding: a scaled or positioned embedding writes one copy")
         if pos_table is not None:
             _need(pos_table, table.dtype, "pos_table", 2); _need(positions, torch.int32, "positions", 1)
             if pos_table.shape[1] != E or not pos_table.is_contiguous() or positions.shape[0] < T:
@@ -224,7 +227,7 @@ def embedding(table, ids, out, err, scale=1.0, pos_table=None, positions=None):
                                              _stream()), "embedding_scaled")
         return
     _check(lib().ferrum_embedding(_ptr(table), dtype_code(table.dtype), _ptr(ids), _ptr(out), c_int(T), c_int(E),
-                                  c_int(V), _ptr(err), _stream()), "embedding")
+                                  c_int(V), _ptr(err), c_int(copies), _stream()), "embedding")
 
 
 class Partials:
@@ -397,7 +400,8 @@ def attention_generic_split():
 
 
 def attention_generic(q, out, n_tokens, positions, req_of_token, block_table, kv_plane, page_stride, page_size, Hq,
-                      Hkv, D, scale, window, err, part=None, split_slots=0, q_start=None, n_reqs=0, distance_penalty=None):
+                      Hkv, D, scale, window, err, part=None, split_slots=0, q_start=None, n_reqs=0, distance_penalty=None,
+                      chunked=False):
     """Causal GQA attention of every token over its request's pages on the CUDA cores, float32
     arithmetic.  part=None: one CTA per (token, group of heads) walks the whole key range (many
     tokens).  With `part` (float32, n_tokens * Hq * split_slots * (D + 2) elements) every row's keys
@@ -406,16 +410,20 @@ def attention_generic(q, out, n_tokens, positions, req_of_token, block_table, kv
     n_reqs + 1 token offsets of the requests, tokens of a request in ascending positions) and no
     `part`, up to eight tokens of a request that follow each other share every tile of keys.
     distance_penalty=(r1, r2), float32 per query head: r1[h] * ln(1 + r2[h] * (position - key position))
-    is taken off the scaled score.  `out` may be float32 whatever the cache's type (a kernel after
-    this one still works on the heads' results)."""
+    is taken off the scaled score; with r2 None it is the straight line r1[h] * (position - key position).
+    chunked: `window` is the length of a chunk (positions are cut into chunks from 0; a query sees its own
+    chunk's keys up to itself) instead of a sliding window.  `out` may be float32 whatever the cache's type
+    (a kernel after this one still works on the heads' results)."""
     _need(q, None, "q", 2); _need(out, None, "out", 2); _need(kv_plane, q.dtype, "kv_plane")
     if out.dtype not in (q.dtype, torch.float32):
         raise KernelError(f"attention: out must be {q.dtype} or float32, found {out.dtype}")
     r1 = r2 = None
     if distance_penalty is not None:
         r1, r2 = distance_penalty
-        _need(r1, torch.float32, "r1", 1); _need(r2, torch.float32, "r2", 1)
-        if r1.shape[0] != Hq or r2.shape[0] != Hq:
+        _need(r1, torch.float32, "r1", 1)
+        if r2 is not None:
+            _need(r2, torch.float32, "r2", 1)
+        if r1.shape[0] != Hq or (r2 is not None and r2.shape[0] != Hq):
             raise KernelError("attention: the distance penalty has one pair of numbers per query head")
     _need(positions, torch.int32, "positions", 1); _need(req_of_token, torch.int32, "req_of_token", 1)
     _need(block_table, torch.int32, "block_table", 2)
@@ -432,7 +440,7 @@ def attention_generic(q, out, n_tokens, positions, req_of_token, block_table, kv
                                           c_float(scale), c_int(window), _ptr(err), _ptr(part), c_int(split_slots),
                                           _ptr(q_start) if part is None else None, c_int(n_reqs), _ptr(r1), _ptr(r2),
                                           c_int(1 if out.dtype == torch.float32 and q.dtype != torch.float32 else 0),
-                                          _stream()),
+                                          c_int(1 if chunked else 0), _stream()),
            "attention_generic")
 
 
@@ -756,11 +764,32 @@ def head_linear(x, x_head_stride, w, y, y_head_stride, n_tokens):
 
 # ----------------------------------------------------------------------------- shaped attention heads
 def qkv_shape(proj, n_tokens, ctx, block_table, rot, qk_pairing, value_rot, value_pairing, unit_norm, eps, q_out, plane,
-              page_stride, page_size, Hq, Hkv, Dk, Dv, Dp, writes):
+              page_stride, page_size, Hq, Hkv, Dk, Dv, Dp, writes, bias=None, q_norm=None, k_norm=None, q_temp=None,
+              value_mix=None):
     """Per head of a float32 product row [q | k | v | ...]: rotary turn of q and k (table `rot`:
     `.cos_sin` [positions, R/2, 2], `.rope_dim`; None: none), optional division by the head's root
     mean square, a turn of the value over all its elements (`value_rot`: a table [positions, Dv/2, 2]
-    or None); q -> q_out [T, Hq * Dp], k and v -> the token's place in the cache (rows of Dp elements)."""
+    or None); q -> q_out [T, Hq * Dp], k and v -> the token's place in the cache (rows of Dp elements).
+    bias: float32 [Hq*Dk + Hkv*(Dk+Dv)] added first.  q_norm / k_norm: float32 [Dk] weights of an RMS norm
+    of every query / key head before the turn.  q_temp = (coef, every): a query at position p is multiplied
+    by 1 + coef * ln(floor((p + 1) / every) + 1).  value_mix = ("store", v_first) leaves the float32 values
+    in v_first [T, Hkv*Dv]; ("blend", v_first, lam) caches (1 - lam) v + lam v_first (lam: one float on the device)."""
+    for t, n in ((bias, Hq * Dk + Hkv * (Dk + Dv)), (q_norm, Dk), (k_norm, Dk)):
+        if t is not None:
+            _need(t, torch.float32, "qkv_shape vector", 1)
+            if t.shape[0] != n or not t.is_contiguous():
+                raise KernelError("qkv_shape: a bias or norm weight has the wrong length")
+    coef, every = q_temp if q_temp is not None else (0.0, 0)
+    mode, v_first, lam = 0, None, None
+    if value_mix is not None:
+        mode = {"store": 1, "blend": 2}[value_mix[0]]
+        v_first = value_mix[1]
+        _need(v_first, torch.float32, "v_first", 2)
+        if v_first.shape[0] < n_tokens or v_first.shape[1] < Hkv * Dv:
+            raise KernelError("qkv_shape: v_first is too small")
+        if mode == 2:
+            lam = value_mix[2]
+            _need(lam, torch.float32, "lambda")
     _need(proj, torch.float32, "proj", 2); _need(q_out, plane.dtype, "q_out", 2); _need(block_table, torch.int32, "block_table", 2)
     if proj.shape[1] < Hq * Dk + (Hkv * (Dk + Dv) if writes else 0) or q_out.shape[1] < Hq * Dp:
         raise KernelError("qkv_shape: a row is too short for the heads")
@@ -771,7 +800,9 @@ def qkv_shape(proj, n_tokens, ctx, block_table, rot, qk_pairing, value_rot, valu
                                   c_int(value_pairing), c_int(value_rot.shape[0] if value_rot is not None else 0),
                                   c_int(1 if unit_norm else 0), c_float(eps), _ptr(q_out), c_int(q_out.stride(0)), _ptr(plane),
                                   c_longlong(page_stride), c_int(page_size), dtype_code(plane.dtype), c_int(Hq), c_int(Hkv),
-                                  c_int(Dk), c_int(Dv), c_int(Dp), c_int(1 if writes else 0), _ptr(ctx.err), _stream()),
+                                  c_int(Dk), c_int(Dv), c_int(Dp), c_int(1 if writes else 0), _ptr(ctx.err), _ptr(bias),
+                                  _ptr(q_norm), _ptr(k_norm), c_float(coef), c_int(every), c_int(mode), _ptr(v_first),
+                                  c_int(v_first.stride(0) if v_first is not None else 0), _ptr(lam), _stream()),
            "qkv_shape")
 
 
@@ -869,3 +900,118 @@ def norm_scaled_add(x, y, w, mult, eps, n_tokens, partials=None):
     _bytes_work((x, 2 * n_tokens), (x, n_tokens))
     _check(lib().ferrum_norm_scaled_add(_ptr(x), _ptr(y if partials is None else None), _ptr(w), c_float(mult), c_float(eps),
                                         c_int(n_tokens), c_int(E), *_partials_args(partials), _stream()), "norm_scaled_add")
+
+
+# ----------------------------------------------------------------------------- several residual streams
+HYPER_MAX_STREAMS = 8        # (the kernel's own limit, which it checks again)
+
+
+class StreamWrite:
+    """What a sublayer leaves for the kernel that reads the streams next: its result (`y` float32 [T, E], or
+    `partials`, or `y` with `y_rows` int32 [T, top] naming the rows to add per token) and its carry matrix
+    `mix` [S, S] and write vector `out` [S] (float32 on the device)."""
+
+    def __init__(self, mix, out, y=None, partials=None, y_rows=None, top=0):
+        self.mix, self.out, self.y, self.partials, self.y_rows, self.top = mix, out, y, partials, y_rows, int(top)
+
+
+def hyper_step(X, S, E, n_rows, write=None, rows=None, store=True, in_w=None, norm_w=None, eps=0.0, out=None):
+    """One pass over the residual streams X [tokens, S * E] (float32): first the pending `write` of the sublayer
+    before (X'[t] = sum_s mix[s, t] X[s] + out[t] y), stored when `store`; then, when `out` is given, the read
+    u = sum_s in_w[s] X[s] (in_w None: the plain sum) and out = rms(u) * norm_w in out's type.  `rows` (int32):
+    work on these tokens only, storing nothing."""
+    _need(X, torch.float32, "X", 2)
+    if X.shape[1] != S * E or not X.is_contiguous():
+        raise KernelError("hyper_step: X must be contiguous [tokens, S * E]")
+    y = ldy = y_rows = part = layout = mix = out_w = None
+    top = 0
+    if write is not None:
+        mix, out_w = write.mix, write.out
+        _need(mix, torch.float32, "mix", 2); _need(out_w, torch.float32, "out", 1)
+        if tuple(mix.shape) != (S, S) or out_w.shape[0] != S or not mix.is_contiguous():
+            raise KernelError("hyper_step: the carry matrix is [S, S], the write vector [S]")
+        if write.partials is not None:
+            part, layout = write.partials.workspace, write.partials._c
+        else:
+            y = write.y
+            _need(y, torch.float32, "y", 2)
+            ldy = y.stride(0)
+            if write.y_rows is not None:
+                y_rows, top = write.y_rows, write.top
+                _need(y_rows, torch.int32, "y_rows")
+    if out is not None:
+        _need(out, None, "out", 2); _need(norm_w, torch.float32, "norm_w", 1)
+        if out.shape[1] != E or out.shape[0] < n_rows or norm_w.shape[0] != E or not out.is_contiguous():
+            raise KernelError("hyper_step: out must be contiguous [>= rows, E]")
+    if in_w is not None:
+        _need(in_w, torch.float32, "in_w", 1)
+    if rows is not None:
+        _need(rows, torch.int32, "rows", 1)
+    global _work
+    if _profile is not None:
+        _work = (n_rows * E * (4 * S * (2 if write is not None and store else 1) + (4 if y is not None else 0)
+                               + (out.element_size() if out is not None else 0)), 0.0)
+    _check(lib().ferrum_hyper_step(_ptr(X), c_int(S), c_int(E), _ptr(rows), c_int(n_rows), _ptr(y), c_int(ldy or 0), _ptr(y_rows),
+                                   c_int(top), _ptr(part), layout, _ptr(mix), _ptr(out_w), c_int(1 if store and rows is None else 0),
+                                   _ptr(in_w), _ptr(norm_w), c_float(eps), _ptr(out),
+                                   dtype_code(out.dtype) if out is not None else c_int(0), _stream()), "hyper_step")
+
+
+# ----------------------------------------------------------------------------- routed feed-forward
+MOE_SCORES = {"sigmoid": 0, "softmax": 1}
+
+
+MOE_MAX_EXPERTS, MOE_MAX_TOP = 256, 8      # (the routing kernel's own limits, which it checks again)
+
+
+def moe_route(logits, n_tokens, n_exp, top, x, scale_input, expert_of, rank_of, weight_of, counts, xg, row_of, scores="sigmoid",
+              renormalize=False):
+    """From the router's float32 logits [T, >= n_exp]: every token's `top` experts and their weights, and the
+    tokens' input rows x [T, E] gathered into xg [T * top, E] sorted by expert (times the weight when
+    `scale_input`); row_of [T * top] says where each (token, choice) went; counts [n_exp] the rows per expert."""
+    global launches
+    _need(logits, torch.float32, "logits", 2); _need(x, None, "x", 2); _need(xg, x.dtype, "xg", 2)
+    for t in (expert_of, rank_of, counts, row_of):
+        _need(t, torch.int32, "routing table")
+    _need(weight_of, torch.float32, "weight_of")
+    E = x.shape[1]
+    if xg.shape[1] != E or xg.shape[0] < n_tokens * top or not xg.is_contiguous() or counts.numel() < n_exp:
+        raise KernelError("moe_route: buffers are too small")
+    _check(lib().ferrum_moe_route(_ptr(logits), c_int(logits.stride(0)), c_int(n_tokens), c_int(n_exp), c_int(top),
+                                  c_int(MOE_SCORES[scores]), c_int(1 if renormalize else 0), _ptr(x), c_int(x.stride(0)), c_int(E),
+                                  dtype_code(x.dtype), c_int(1 if scale_input else 0), _ptr(expert_of), _ptr(rank_of),
+                                  _ptr(weight_of), _ptr(counts), _ptr(xg), _ptr(row_of), _stream()), "moe_route")
+    launches += 1          # (the entry point launches the routing and the gather)
+
+
+def moe_gemm(a, w, counts, n_rows, out, N, glu=None):
+    """out[row] = a[row] @ w[expert of row].T over rows sorted by expert (`counts` rows each, on the device).
+    w: [n_exp, rows, K]; glu ("silu" / "gelu_tanh"): w holds N gate rows then N up rows per expert and out
+    (compute type) gets act(gate) * up; else out is float32 [n_rows, N]."""
+    _need(a, None, "a", 2); _need(w, a.dtype, "w", 3); _need(out, a.dtype if glu else torch.float32, "out", 2)
+    n_exp, w_rows, K = w.shape
+    if not w.is_contiguous() or a.shape[1] != K or a.shape[0] < n_rows or out.shape[0] < n_rows or out.shape[1] < N:
+        raise KernelError("moe_gemm: shapes do not agree")
+    global _work
+    if _profile is not None:
+        _work = (w.numel() * w.element_size() + n_rows * (K * a.element_size() + N * out.element_size()),
+                 2.0 * n_rows * K * N * (2 if glu else 1))
+    _check(lib().ferrum_moe_gemm(_ptr(a), c_int(a.stride(0)), _ptr(w), c_int(w_rows), c_int(K), c_int(N), c_int(n_exp), _ptr(counts),
+                                 c_int(n_rows), dtype_code(a.dtype), c_int(1 if glu else 0), c_int(GLU_ACTS[glu] if glu else 0),
+                                 _ptr(out), c_int(out.stride(0)), _stream()), "moe_gemm")
+
+
+def moe_combine(rows, row_of, top, n_tokens, y, weight_of=None):
+    """y[t] = sum_j rows[row_of[t, j]] (times weight_of[t, j] when given), float32."""
+    _need(rows, torch.float32, "rows", 2); _need(y, torch.float32, "y", 2); _need(row_of, torch.int32, "row_of")
+    E = y.shape[1]
+    if not y.is_contiguous() or rows.shape[1] < E:
+        raise KernelError("moe_combine: shapes do not agree")
+    _check(lib().ferrum_moe_combine(_ptr(rows), c_int(rows.stride(0)), _ptr(row_of), _ptr(weight_of), c_int(top), c_int(n_tokens),
+                                    c_int(E), _ptr(y), _stream()), "moe_combine")
+
+
+def softcap(x, n_rows, cap):
+    """x[:n_rows] <- cap * tanh(x / cap) in place (float32)."""
+    _need(x, torch.float32, "x", 2)
+    _check(lib().ferrum_softcap(_ptr(x), c_int(x.stride(0)), c_int(n_rows), c_int(x.shape[1]), c_float(cap), _stream()), "softcap")

@@ -1,10 +1,11 @@
 from .attention import PagedAttention
 from .base import (CacheNeed, FeedForward, Mixer, Norm, PagedKVNeed, ParamSpec, Part, PositionEncoding,
                    StateNeed)
-from .block import ParallelBlock, ParallelGatedBlock, PreNormBlock, TokenSideInput, TokenSideTable
+from .block import (ParallelBlock, ParallelGatedBlock, PreNormBlock, StreamBlock, StreamSumNorm, TokenSideInput,
+                    TokenSideTable)
 from .embedding import LearnedPositions, OutputHead, TokenEmbedding
 from .latent_attention import LatentAttention
-from .ffn import SwiGLU
+from .ffn import RoutedFeedForward, SwiGLU
 from .mamba2 import Mamba2Mixer
 from .shaped_attention import ShapedAttention
 from .norm import RMSNorm
@@ -12,4 +13,5 @@ from .rope import RotaryEmbedding
 
 __all__ = ["PagedAttention", "CacheNeed", "FeedForward", "Mixer", "Norm", "PagedKVNeed", "ParamSpec", "Part",
            "PositionEncoding", "StateNeed", "PreNormBlock", "ParallelGatedBlock", "LatentAttention", "LearnedPositions", "OutputHead", "TokenEmbedding", "SwiGLU", "RMSNorm",
-           "RotaryEmbedding", "ParallelBlock", "TokenSideInput", "TokenSideTable", "Mamba2Mixer", "ShapedAttention"]
+           "RotaryEmbedding", "ParallelBlock", "TokenSideInput", "TokenSideTable", "Mamba2Mixer", "ShapedAttention", "StreamBlock", "StreamSumNorm",
+           "RoutedFeedForward"]

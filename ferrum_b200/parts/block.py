@@ -265,3 +265,113 @@ class ParallelBlock(Part):
         ops.scaled_sum(h, y1, y2, self.mult, T, xc, p1=p1, p2=p2)
         if self.side is not None:
             self.side.forward(h, xc if xc is not None else h, ctx, self.mult)
+
+
+def _stream_init(kind):
+    """Random-weights draws for a block's stream tensors: values near the ones that make the block a plain
+    pre-norm block (read: equal shares; carry: the identity; write: ones), so that a random model stays tame."""
+    def draw(shape, g, device, std):
+        noise = torch.randn(shape, generator=g, device=device, dtype=torch.float32) * 0.1
+        if kind == "in":
+            return 1.0 / shape[0] + noise
+        if kind == "mix":
+            return torch.eye(shape[0], device=device, dtype=torch.float32) + noise
+        return 1.0 + noise
+    return draw
+
+
+class StreamBlock(Part):
+    """A pre-norm block over S copies X[0..S-1] of the residual stream (one row of S * width floats per
+    token).  Sublayer q (the mixer, then the feed-forward) owns a read vector a_q [S], a carry matrix
+    M_q [S, S] (indexed [from, to]) and a write vector b_q [S]:
+
+        u = sum_s a_q[s] X[s];   y = sublayer(norm_q(u));   X'[t] = sum_s M_q[s, t] X[s] + b_q[t] y
+
+    (all t at once, from the old rows).  With S = 1, a = [1], M = [[1]], b = [1] this is `PreNormBlock`.
+    One kernel applies the write of the sublayer before it and makes the read and the norm of the next,
+    so a sublayer's write stays pending in `ctx` (`StepContext.pending_streams`) until the next reader of
+    the rows; a sublayer's last product may stay in partials for that kernel, and a routed feed-forward
+    hands over its experts' result rows unsummed.  `ffn` may be None.  The model's embedding writes S
+    copies of a token's row (`TokenEmbedding(copies=S)`), its last norm is a `StreamSumNorm`."""
+    graph_safe = True
+
+    def __init__(self, streams, norm1: Norm, mixer: Mixer, norm2: Norm = None, ffn: FeedForward = None,
+                 names=("norm1.", "mix.", "norm2.", "mlp.")):
+        if not 1 <= streams <= ops.HYPER_MAX_STREAMS:
+            raise ValueError(f"{streams} residual streams are outside 1..{ops.HYPER_MAX_STREAMS}")
+        if (norm2 is None) != (ffn is None):
+            raise ValueError("the second norm and the feed-forward come together")
+        self.streams, self.width = int(streams), norm1.width
+        self.norm1, self.mixer, self.norm2, self.ffn = norm1, mixer, norm2, ffn
+        self._names = names
+        self.w_hc1_in = self.w_hc1_mix = self.w_hc1_out = self.w_hc2_in = self.w_hc2_mix = self.w_hc2_out = None
+
+    def param_specs(self):
+        S = self.streams
+        out = {}
+        lone = S == 1           # (a file of a model with one stream may leave them out: the plain pre-norm block)
+        for q in ("hc1", "hc2") if self.ffn is not None else ("hc1",):
+            out.update({q + ".in": ParamSpec((S,), kind="vector", init=_stream_init("in"), optional=lone),
+                        q + ".mix": ParamSpec((S, S), kind="vector", init=_stream_init("mix"), optional=lone),
+                        q + ".out": ParamSpec((S,), kind="vector", init=_stream_init("out"), optional=lone)})
+        return out
+
+    def finalize(self):
+        super().finalize()
+        device = self.norm1.w_weight.device
+        for q in ("hc1", "hc2") if self.ffn is not None else ("hc1",):
+            for k, shape in (("in", (1,)), ("mix", (1, 1)), ("out", (1,))):
+                if getattr(self, f"w_{q}_{k}") is None:
+                    setattr(self, f"w_{q}_{k}", torch.ones(shape, dtype=torch.float32, device=device))
+
+    def children(self):
+        out = [(self._names[0], self.norm1), (self._names[1], self.mixer)]
+        if self.ffn is not None:
+            out += [(self._names[2], self.norm2), (self._names[3], self.ffn)]
+        return out
+
+    def forward(self, h, ctx, cache):
+        S, E, T, cap = self.streams, self.width, ctx.n_tokens, ctx.token_capacity
+        few = T <= OVERLAP_MAX_TOKENS
+        x = ctx.buf("stream_x", (cap, E), self.norm1.out_dtype)
+        ops.hyper_step(h, S, E, T, write=ctx.take_pending_streams(h), in_w=self.w_hc1_in, norm_w=self.norm1.w_weight,
+                       eps=self.norm1.eps, out=x)
+        y = ctx.buf("stream_y", (cap, E), torch.float32)
+        part = self.mixer.forward(x, ctx, cache, y, accumulate=False, defer=few)
+        write = ops.StreamWrite(self.w_hc1_mix, self.w_hc1_out, y=y if part is None else None, partials=part)
+        if self.ffn is None:
+            ctx.pending_streams = (h, S, E, write)
+            return
+        ops.hyper_step(h, S, E, T, write=write, in_w=self.w_hc2_in, norm_w=self.norm2.w_weight, eps=self.norm2.eps, out=x)
+        if hasattr(self.ffn, "forward_rows"):
+            rows, row_of, top = self.ffn.forward_rows(x, ctx)
+            write = ops.StreamWrite(self.w_hc2_mix, self.w_hc2_out, y=rows, y_rows=row_of, top=top)
+        else:
+            part = self.ffn.forward(x, ctx, y, accumulate=False, defer=few)
+            write = ops.StreamWrite(self.w_hc2_mix, self.w_hc2_out, y=y if part is None else None, partials=part)
+        ctx.pending_streams = (h, S, E, write)
+
+
+class StreamSumNorm(Norm):
+    """The last norm of a model whose blocks are `StreamBlock`s: an RMS norm of the plain sum of a token's
+    S streams, after the last sublayer's pending write (applied to the asked rows only, stored nowhere)."""
+    graph_safe = True
+
+    def __init__(self, streams, width: int, eps: float, out_dtype):
+        self.streams, self.width, self.eps, self.out_dtype = int(streams), width, float(eps), out_dtype
+        self.w_weight = None
+
+    def param_specs(self):
+        return {"weight": ParamSpec((self.width,), kind="vector", init="ones_normal")}
+
+    def forward(self, h, ctx, rows=None, n_rows=None, tag="norm"):
+        n = n_rows if n_rows is not None else ctx.n_tokens
+        cap = ctx.want_capacity if rows is not None else ctx.token_capacity
+        out = ctx.buf(tag + ("_rows" if rows is not None else ""), (cap, self.width), self.out_dtype)
+        write = ctx.take_pending_streams(h)
+        if write is not None and rows is None:
+            # every row is read: store the write first, then read
+            ops.hyper_step(h, self.streams, self.width, ctx.n_tokens, write=write, store=True)
+            write = None
+        ops.hyper_step(h, self.streams, self.width, n, write=write, rows=rows, store=False, norm_w=self.w_weight, eps=self.eps, out=out)
+        return out

@@ -18,20 +18,23 @@ from .linear import STORE_F32, linear
 class TokenEmbedding(Part):
     graph_safe = True
 
-    def __init__(self, n_vocab, width, scale=1.0, positions: "LearnedPositions" = None):
+    def __init__(self, n_vocab, width, scale=1.0, positions: "LearnedPositions" = None, copies=1):
         """positions: a `LearnedPositions` part whose vector for a token's position is added to the
-        (scaled) embedding; the model lists it as its position encoding, which owns the table."""
+        (scaled) embedding; the model lists it as its position encoding, which owns the table.
+        copies > 1: the residual rows are [tokens, copies * width], every copy the embedded token (a
+        model whose blocks keep several residual streams)."""
         self.n_vocab, self.width, self.scale, self.positions = n_vocab, width, float(scale), positions
+        self.copies = int(copies)
         self.w_weight = None
 
     def param_specs(self):
         return {"weight": ParamSpec((self.n_vocab, self.width))}
 
     def forward(self, ctx):
-        h = ctx.buf("hidden", (ctx.token_capacity, self.width), torch.float32)
+        h = ctx.buf("hidden", (ctx.token_capacity, self.copies * self.width), torch.float32)
         pos = self.positions.w_weight if self.positions is not None else None
         ops.embedding(self.w_weight, ctx.token_ids, h, ctx.err, scale=self.scale, pos_table=pos,
-                      positions=ctx.positions if pos is not None else None)
+                      positions=ctx.positions if pos is not None else None, copies=self.copies)
         return h
 
 
@@ -52,10 +55,12 @@ class LearnedPositions(PositionEncoding):
 class OutputHead(Part):
     graph_safe = True
 
-    def __init__(self, n_vocab, width, tied_to: TokenEmbedding = None, tied="auto"):
+    def __init__(self, n_vocab, width, tied_to: TokenEmbedding = None, tied="auto", softcap=0.0):
         """tied: True (no matrix of its own), False (must have one), "auto" (use the file's
-        matrix when present, else the embedding: the reference's rule)."""
+        matrix when present, else the embedding: the reference's rule).  softcap c > 0: the logits
+        leave as c * tanh(logits / c)."""
         self.n_vocab, self.width, self.tied_to, self.tied = n_vocab, width, tied_to, tied
+        self.softcap = float(softcap or 0.0)
         self.w_weight = None
 
     def param_specs(self):
@@ -72,4 +77,6 @@ class OutputHead(Part):
     def forward(self, x, ctx, n_rows):
         logits = ctx.buf("logits", (ctx.want_capacity, self.n_vocab), torch.float32)
         linear(x, self.w_weight, logits, STORE_F32, ctx, M=n_rows)
+        if self.softcap > 0.0:
+            ops.softcap(logits, n_rows, self.softcap)
         return logits

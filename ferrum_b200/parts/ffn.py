@@ -9,7 +9,8 @@ crates/model/src/weights.rs:165-167): gate and up then leave their product in fl
 kernel adds the biases and applies the activation, and the down bias is either added by a block
 that sums the sublayer's result itself (`accumulate=False`; it reads `down_bias`) or, when the
 part adds into the residual stream, is not supported.  `act` names the activation of the gate
-("silu" or "gelu_tanh").  `extra_rows` appends further weight rows to the gate/up matrix: a
+("silu" or "gelu_tanh"); another activation than silu takes the same float32 gate/up path, with or
+without biases.  `extra_rows` appends further weight rows to the gate/up matrix: a
 block that needs another product of the same input gets it from the same launch
 (`forward(..., extra_out=...)` returns a view of those columns).
 """
@@ -31,8 +32,6 @@ class SwiGLU(FeedForward):
         activation's input is rounded nowhere; without it that path stores them in the compute type."""
         if act not in ops.GLU_ACTS:
             raise ValueError(f"unknown activation {act!r}")
-        if act != "silu" and not bias:
-            raise ValueError("the fused gate/up kernels apply silu; another activation runs on the biased path")
         self.width, self.hidden, self.dtype, self.bias, self.act = width, hidden, dtype, bool(bias), act
         self.wide_products = bool(wide_products)
         self.w_gate_weight = self.w_up_weight = self.w_down_weight = None
@@ -67,8 +66,8 @@ class SwiGLU(FeedForward):
     def forward(self, x, ctx, residual, accumulate=True, defer=False):
         F, T = self.hidden, ctx.n_tokens
         act = ctx.buf("ffn_act", (ctx.token_capacity, F), self.dtype)
-        if self.bias:
-            if accumulate:
+        if self.bias or self.act != "silu":       # (the fused gate/up kernels apply silu and add no bias)
+            if self.bias and accumulate:
                 raise ValueError("a biased feed-forward hands its result to a block that adds the down bias")
             n = self.w_gate_up.shape[0]
             # a few tokens: the product stays in partials and the activation kernel sums them
@@ -96,4 +95,80 @@ class SwiGLU(FeedForward):
             if part is not None:
                 return part
         linear(act, self.w_down_weight, residual, RESIDUAL if accumulate else STORE_F32, ctx, M=T)
+        return None
+
+
+class RoutedFeedForward(FeedForward):
+    """A mixture of experts: every token runs through `top` of `n_experts` small gated feed-forwards
+    down_e(act(gate_e z) * (up_e z)), chosen by a router.
+
+    router logits   W_router x in float32 (x in the compute type)
+    scores          "sigmoid" of each logit, or "softmax" over all experts
+    choice          the `top` largest scores (a tie goes to the lower index)
+    weights         the chosen scores, divided by their sum when `renormalize`
+    scale_input     True: an expert sees z = weight * x and its result is added as it is;
+                    False: it sees x and its result is multiplied by the weight
+
+    The tokens' rows are gathered into a buffer sorted by expert; two grouped products (gate/up with
+    the activation, then down) run over it with the experts' stacked matrices, every CTA finding its
+    expert from per-expert counters on the device, so a step's launches depend on the batch's sizes
+    only.  `forward_rows` hands the unsummed result rows to a block that adds them itself;
+    `forward(accumulate=False)` sums them into the block's buffer."""
+    graph_safe = True
+
+    def __init__(self, width, hidden, n_experts, top, dtype, act="silu", scores="sigmoid", renormalize=False, scale_input=True):
+        if act not in ops.GLU_ACTS:
+            raise ValueError(f"unknown activation {act!r}")
+        if scores not in ops.MOE_SCORES:
+            raise ValueError(f"unknown router scores {scores!r}")
+        if not (0 < top <= n_experts <= ops.MOE_MAX_EXPERTS and top <= ops.MOE_MAX_TOP):
+            raise ValueError(f"{top} of {n_experts} experts per token are outside the routing kernel's limits "
+                             f"({ops.MOE_MAX_TOP} of {ops.MOE_MAX_EXPERTS})")
+        self.width, self.hidden, self.n_experts, self.top, self.dtype = width, hidden, int(n_experts), int(top), dtype
+        self.act, self.scores, self.renormalize, self.scale_input = act, scores, bool(renormalize), bool(scale_input)
+        self.w_router_weight = self.w_gate_up = self.w_down = None
+
+    def param_specs(self):
+        out = {"router.weight": ParamSpec((self.n_experts, self.width))}
+        for e in range(self.n_experts):
+            out.update({f"e{e}.gate.weight": ParamSpec((self.hidden, self.width)),
+                        f"e{e}.up.weight": ParamSpec((self.hidden, self.width)),
+                        f"e{e}.down.weight": ParamSpec((self.width, self.hidden))})
+        return out
+
+    def finalize(self):
+        def take(name):
+            t = getattr(self, name)
+            delattr(self, name)
+            return t
+        gu = [torch.cat([take(f"w_e{e}_gate_weight"), take(f"w_e{e}_up_weight")], dim=0) for e in range(self.n_experts)]
+        self.w_gate_up = torch.stack(gu, dim=0).contiguous()                       # [experts, 2F, E]
+        self.w_down = torch.stack([take(f"w_e{e}_down_weight") for e in range(self.n_experts)], dim=0).contiguous()   # [experts, E, F]
+
+    def forward_rows(self, x, ctx):
+        """(rows float32 [T * top, width], row_of int32 [T * top], top): token t's result is the sum over j of
+        rows[row_of[t * top + j]] (already weighted when the weight scales the expert's input)."""
+        T, cap, top, n = ctx.n_tokens, ctx.token_capacity, self.top, self.n_experts
+        logits = ctx.buf("moe_logits", (cap, n), torch.float32)
+        linear(x, self.w_router_weight, logits, STORE_F32, ctx, M=T)
+        expert_of = ctx.buf("moe_expert_of", (cap * top,), torch.int32)
+        rank_of = ctx.buf("moe_rank_of", (cap * top,), torch.int32)
+        row_of = ctx.buf("moe_row_of", (cap * top,), torch.int32)
+        weight_of = ctx.buf("moe_weight_of", (cap * top,), torch.float32)
+        counts = ctx.buf("moe_counts", (n,), torch.int32)
+        xg = ctx.buf("moe_x", (cap * top, self.width), self.dtype)
+        ops.moe_route(logits, T, n, top, x, self.scale_input, expert_of, rank_of, weight_of, counts, xg, row_of,
+                      scores=self.scores, renormalize=self.renormalize)
+        act = ctx.buf("moe_act", (cap * top, self.hidden), self.dtype)
+        ops.moe_gemm(xg, self.w_gate_up, counts, T * top, act, self.hidden, glu=self.act)
+        rows = ctx.buf("moe_rows", (cap * top, self.width), torch.float32)
+        ops.moe_gemm(act, self.w_down, counts, T * top, rows, self.width)
+        self._weight_of = weight_of
+        return rows, row_of, top
+
+    def forward(self, x, ctx, residual, accumulate=True, defer=False):
+        if accumulate:
+            raise ValueError("a routed feed-forward hands its result to a block that adds it")
+        rows, row_of, top = self.forward_rows(x, ctx)
+        ops.moe_combine(rows, row_of, top, ctx.n_tokens, residual, weight_of=None if self.scale_input else self._weight_of)
         return None

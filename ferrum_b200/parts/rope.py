@@ -57,7 +57,13 @@ def llama3_scaling(f, scaling):
     return out
 
 
+def linear_scaling(f, scaling):
+    """Every frequency divided by `factor` (positions stretched by it)."""
+    return [fk / float(scaling.factor) for fk in f]
+
+
 register_scaling("llama3", llama3_scaling)
+register_scaling("linear", linear_scaling)
 
 
 class RotaryEmbedding(PositionEncoding):

@@ -9,8 +9,20 @@ What a configuration may switch on, each with its constants as parameters:
                  every head's result at position i turns back by i (a `RotaryEmbedding` over vdim)
   distance_penalty   r1[h] * ln(1 + r2[h] * (i - j)) is taken off the scaled score (r1, r2: tensors)
   gate           the heads' results are multiplied by sigmoid(W_g x) before the output projection
-  window         a query sees itself and the window - 1 keys before it (0: all)
+  window         a query sees itself and the window - 1 keys before it (0: all); with mask="chunk"
+                 positions are cut into chunks of `window` from position 0 and a query sees the keys of
+                 its own chunk up to itself
   dim != vdim    key and value heads of different sizes share pages of max(dim, vdim)-element rows
+  qkv_bias       q, k and v projections have bias vectors
+  qk_norm        every q and k head is divided by its root mean square and multiplied by a weight
+                 vector shared by all heads, BEFORE the turn
+  query_temperature  (coef, every): a query at position p is multiplied by
+                 1 + coef * ln(floor((p + 1) / every) + 1)
+  linear_bias    per-head slopes m[h]: m[h] * (i - j) is taken off the scaled score (numbers, not tensors)
+  value_mix      "first": this layer leaves its values (float32, before rounding) in a buffer of the
+                 step named `value_mix_key`; "blend": its values become (1 - lambda) v + lambda v_first
+                 with the scalar tensor `vmix` before they are cached.  The layers that share a key
+                 must agree on kv heads x vdim.
 
 Scores, softmax weights, the weighted sum, rotations, the unit norm and the gate are float32 whatever
 the compute type (the CUDA-core attention kernel; keys, values and queries are stored in the compute
@@ -33,11 +45,30 @@ class ShapedAttention(PagedAttention):
     graph_safe = True       # the CUDA-core attention kernel reads no work lists
 
     def __init__(self, width, n_head, n_head_kv, dim, vdim, dtype, scale, eps=1e-6, window=0, rotary=None, unit_norm=False,
-                 value_rotary=None, distance_penalty=False, gate=False):
+                 value_rotary=None, distance_penalty=False, gate=False, mask="window", qkv_bias=False, qk_norm=False,
+                 query_temperature=None, linear_bias=None, value_mix=None, value_mix_key="v_first"):
         super().__init__(width, n_head, n_head_kv, max(int(dim), int(vdim)), rotary, dtype, window=window, scale=scale)
         self.Dk, self.Dv, self.eps = int(dim), int(vdim), float(eps)
         self.unit_norm, self.value_rotary = bool(unit_norm), value_rotary
         self.has_penalty, self.has_gate = bool(distance_penalty), bool(gate)
+        if mask not in ("window", "chunk"):
+            raise ValueError(f"unknown mask {mask!r}")
+        self.chunked = mask == "chunk" and self.window > 0
+        self.has_bias, self.qk_norm = bool(qkv_bias), bool(qk_norm)
+        self.q_temp = None
+        if query_temperature is not None:
+            coef, every = float(query_temperature[0]), int(query_temperature[1])
+            if every <= 0:
+                raise ValueError("the query temperature's step must be positive")
+            self.q_temp = (coef, every)
+        self.linear_bias = [float(v) for v in linear_bias] if linear_bias is not None else None
+        if self.linear_bias is not None and (len(self.linear_bias) != n_head or self.has_penalty):
+            raise ValueError("a linear distance bias has one slope per query head and excludes the logarithmic penalty")
+        if value_mix not in (None, "first", "blend"):
+            raise ValueError(f"unknown value mixing role {value_mix!r}")
+        self.value_mix, self.value_mix_key = value_mix, str(value_mix_key)
+        self.w_q_bias = self.w_k_bias = self.w_v_bias = self.w_q_norm_weight = self.w_k_norm_weight = self.w_vmix = None
+        self.w_bias = self.slopes = None
         if rotary is not None and rotary.rope_dim > self.Dk:
             raise ValueError("the rotary table turns more elements than a key head has")
         if value_rotary is not None and value_rotary.rope_dim != self.Dv:
@@ -54,12 +85,27 @@ class ShapedAttention(PagedAttention):
             out["r2"] = ParamSpec((self.Hq,), kind="vector", init="uniform")
         if self.has_gate:
             out["g.weight"] = ParamSpec((self.Hq * self.Dv, E))
+        if self.has_bias:
+            out.update({"q.bias": ParamSpec((self.Hq * self.Dk,), kind="vector"), "k.bias": ParamSpec((self.Hkv * self.Dk,), kind="vector"),
+                        "v.bias": ParamSpec((self.Hkv * self.Dv,), kind="vector")})
+        if self.qk_norm:
+            out.update({"q.norm.weight": ParamSpec((self.Dk,), kind="vector", init="ones_normal"),
+                        "k.norm.weight": ParamSpec((self.Dk,), kind="vector", init="ones_normal")})
+        if self.value_mix is not None:
+            out["vmix"] = ParamSpec((), kind="vector", init="uniform")      # (read by the blending layers only)
         return out
 
     def finalize(self):
         rows = [self.w_q_weight, self.w_k_weight, self.w_v_weight] + ([self.w_g_weight] if self.has_gate else [])
         self.w_in = torch.cat(rows, dim=0).contiguous()
         self.w_q_weight = self.w_k_weight = self.w_v_weight = self.w_g_weight = None
+        if self.has_bias:
+            self.w_bias = torch.cat([self.w_q_bias, self.w_k_bias, self.w_v_bias]).contiguous()
+            self.w_q_bias = self.w_k_bias = self.w_v_bias = None
+        if self.linear_bias is not None:
+            self.slopes = torch.tensor(self.linear_bias, dtype=torch.float32, device=self.w_in.device)
+        if self.w_vmix is not None:
+            self.w_vmix = self.w_vmix.reshape(1).contiguous()
 
     def cache_need(self):
         return CacheNeed(paged=PagedKVNeed(self.Hkv, self.D, self.window))
@@ -75,11 +121,18 @@ class ShapedAttention(PagedAttention):
         table = ctx.block_tables[cache.group]
         q = ctx.buf("sattn_q", (cap, Hq * Dp), self.dtype)
         rot, vrot = self.position, self.value_rotary
+        mix = None
+        if self.value_mix is not None and cache.writes:
+            first = ctx.buf(self.value_mix_key, (cap, Hkv * Dv), torch.float32)
+            mix = ("store", first) if self.value_mix == "first" else ("blend", first, self.w_vmix)
         ops.qkv_shape(proj, T, ctx, table, rot, rot.pairing if rot is not None else 0,
                       vrot.cos_sin if vrot is not None else None, vrot.pairing if vrot is not None else 0, self.unit_norm,
-                      self.eps, q, cache.plane, cache.page_stride, cache.page_size, Hq, Hkv, Dk, Dv, Dp, cache.writes)
+                      self.eps, q, cache.plane, cache.page_stride, cache.page_size, Hq, Hkv, Dk, Dv, Dp, cache.writes,
+                      bias=self.w_bias, q_norm=self.w_q_norm_weight if self.qk_norm else None,
+                      k_norm=self.w_k_norm_weight if self.qk_norm else None, q_temp=self.q_temp, value_mix=mix)
         o = ctx.buf("sattn_o", (cap, Hq * Dp), torch.float32)
-        self._generic(q, o, ctx, cache, table, (self.w_r1, self.w_r2) if self.has_penalty else None)
+        penalty = (self.w_r1, self.w_r2) if self.has_penalty else ((self.slopes, None) if self.slopes is not None else None)
+        self._generic(q, o, ctx, cache, table, penalty)
         out = ctx.buf("sattn_out", (cap, Hq * Dv), self.dtype)
         off = Hq * Dk + Hkv * (Dk + Dv)
         gate = proj[:, off:off + Hq * Dv] if self.has_gate else None

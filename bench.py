@@ -3,7 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
                     [--model llama31-8b|llama32-3b|llama2-7b] [--dtype bf16|fp16|fp32]
-                    [--workload decode|serve|latent|hybrid] [--layers L] [--batch B] [--context S] [--trials N] [--size 2b|8b]
+                    [--workload decode|serve|latent|hybrid|streams] [--layers L] [--batch B] [--context S] [--trials N] [--size 2b|8b]
 
 Prints ONE JSON line.
 
@@ -34,6 +34,13 @@ of the measured roofline.  `value` is the design's decode rate.
 unit-norm heads and turned values, a Mamba-2 mixer, windowed attention with a distance penalty and a
 gate, a Mamba-2 mixer; parallel blocks with a per-layer token input) beside a Llama of equal width,
 heads, feed-forward width and layers.
+
+`--workload streams`: the same comparison for the Zavesun design (four residual streams around every
+sublayer; layers in turn: windowed attention with distance slopes and a query temperature + dense
+feed-forward, chunked rotary attention with biased, normed heads + eight experts of which a token takes
+two, windowed + experts, chunked + dense; values blended with the first layer's; tied output matrix with
+a soft cap) beside a Llama of equal width, heads, KV heads, layers and feed-forward width (the two chosen
+experts together are as wide as the dense feed-forward).
 
 Weights are random N(0, 0.02); token ids are uniform random from a seed.  No L2 flush is needed
 between steps: a step reads gigabytes of weights, far more than the 126 MB L2 holds.
@@ -180,8 +187,8 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (named in config)")
     ap.add_argument("--model", default="llama31-8b", choices=sorted(MODELS), help="layer sizes (random weights)")
     ap.add_argument("--dtype", default="bf16", choices=sorted(DTYPES), help="compute dtype; fp32 is the true 32-bit path")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serve", "latent", "hybrid"])
-    ap.add_argument("--size", default="2b", choices=sorted(LATENT_SIZES), help="latent, hybrid: the layer sizes to compare at")
+    ap.add_argument("--workload", default="decode", choices=["decode", "serve", "latent", "hybrid", "streams"])
+    ap.add_argument("--size", default="2b", choices=sorted(LATENT_SIZES), help="latent, hybrid, streams: the layer sizes to compare at")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=None,
                     help="cached tokens per request of the headline point (default 8192 for llama31-8b, 4096 for "
@@ -204,6 +211,8 @@ def main():
         return latent(args)
     if args.workload == "hybrid":
         return latent(args, design="vikupel")
+    if args.workload == "streams":
+        return latent(args, design="zavesun")
     return decode(args)
 
 
@@ -544,6 +553,37 @@ def hybrid_configs(size, layers, vocab=32000, window=1024):
     return ours, llama
 
 
+# Zavesun at the same two widths: heads of 128 (a quarter as many KV heads), four residual streams, eight experts
+# half as wide as the dense feed-forward, two per token.
+STREAM_SIZES = {
+    "2b": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, ff=5632, experts=8, top=2, expert_ff=2816, streams=4),
+    "8b": dict(width=4096, heads=32, kv_heads=8, dim=128, vdim=128, ff=14336, experts=8, top=2, expert_ff=7168, streams=4),
+}
+
+
+def stream_configs(size, layers, vocab=32000, window=1024):
+    """Layers in turn: windowed + dense, chunked + experts, windowed + experts, chunked + dense; and the Llama beside it."""
+    s = STREAM_SIZES[size]
+    att = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["vdim"], "scale": s["dim"] ** -0.5,
+           "mask": {"size": window}, "v_mix": True}
+    windowed = {"type": "attention", "mixer": dict(att, q_temp={"coef": 0.5, "every": 128})}
+    chunked = {"type": "attention_2", "mixer": dict(att, rot={"base": 10000.0, "dims": s["dim"] // 2, "scaling": {"factor": 8.0}})}
+    dense = {"kind": "dense", "ff": s["ff"]}
+    routed = {"kind": "moe", "expert": {"ff": s["expert_ff"]}, "router": {"experts": s["experts"], "top": s["top"]}}
+    kinds = [dict(windowed, mlp=dense), dict(chunked, mlp=routed), dict(windowed, mlp=routed), dict(chunked, mlp=dense)]
+    ours = {"architecture": "Zavesun", "vocab": vocab, "width": s["width"], "norm": {"eps": 1e-6}, "streams": s["streams"],
+            "logit_softcap": 30.0, "layers": [kinds[i % 4] for i in range(layers)]}
+    llama = {"architectures": ["LlamaForCausalLM"], "hidden_size": s["width"], "num_hidden_layers": layers,
+             "num_attention_heads": s["heads"], "num_key_value_heads": s["kv_heads"], "head_dim": 128,
+             "intermediate_size": s["ff"], "vocab_size": vocab, "rope_theta": 10000.0, "max_position_embeddings": 4096,
+             "rms_norm_eps": 1e-6, "tie_word_embeddings": False}
+    return ours, llama
+
+
+DESIGNS = {"ruperax": ("Ruperax", latent_configs, LATENT_SIZES, 4096), "vikupel": ("Vikupel", hybrid_configs, HYBRID_SIZES, 1024),
+           "zavesun": ("Zavesun", stream_configs, STREAM_SIZES, 1024)}
+
+
 def latent(args, design="ruperax"):
     """Prefill (one 2048-token prompt in one step) and decode (batch 8 at 2048 cached tokens) of the
     Ruperax design at real layer sizes beside a Llama of equal size, random weights, and per kernel
@@ -567,7 +607,8 @@ def latent(args, design="ruperax"):
     gen = torch.Generator().manual_seed(0)
     out = {}
     with ClockSampler() as clk:
-        configs = latent_configs(args.size, L) if design == "ruperax" else hybrid_configs(args.size, L)
+        title, make_configs, all_sizes, window = DESIGNS[design]
+        configs = make_configs(args.size, L)
         for name, cfgd in zip((design, "llama"), configs):
             arch = registry.lookup(registry.architecture_name(cfgd))
             cfg = arch.read_config(cfgd)
@@ -642,14 +683,13 @@ def latent(args, design="ruperax"):
             gc.collect()
             torch.cuda.empty_cache()
     ours = out[design]
-    title = {"ruperax": "Ruperax", "vikupel": "Vikupel"}[design]
-    sizes = LATENT_SIZES[args.size] if design == "ruperax" else HYBRID_SIZES[args.size]
+    sizes = all_sizes[args.size]
     line = {"metric": f"decode tok/s ({title} {args.size} layer sizes, {args.dtype}, batch {B}, context {ctx_len})",
             "value": ours["decode_tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W,
             "ms_per_step": ours["decode_ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": args.dtype, "data": "synthetic", "impl": "ours",
             "config": dict(sizes, model=f"{title}, {args.size} layer sizes, random weights", layers=L,
-                           global_batch=B, seq_len=ctx_len, prefill_tokens=T, window=4096 if design == "ruperax" else 1024,
+                           global_batch=B, seq_len=ctx_len, prefill_tokens=T, window=window,
                            vocab=32000, page_size=page,
                            parallelism="single GPU", l2="weights of a step exceed the L2 at these sizes"),
             "clocks": clk.summary(), "gpu_launches": int(ours["decode_launches_per_step"] * K), "peaks": pk,

@@ -109,7 +109,7 @@ def write_safetensors(path: str, tensors: Dict[str, torch.Tensor], metadata=None
         t = tensors[name].detach().cpu().contiguous()
         if t.dtype not in _NAMES:
             raise FileFormatError(f"cannot store dtype {t.dtype} of {name}")
-        raw = t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
+        raw = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""     # (reshape: a scalar has no byte view)
         header[name] = {"dtype": _NAMES[t.dtype], "shape": list(t.shape),
                         "data_offsets": [offset, offset + len(raw)]}
         offset += len(raw)

@@ -207,10 +207,23 @@ def router_choice(h, w_router, top, round_to):
     return idx, w
 
 
-def routed_ff(h, W, p, mlp, round_to):
-    """sum over a token's chosen experts of expert(weight * h); expert = down(silu(gate z) * (up z))."""
+def router_margin(h, w_router, top, round_to):
+    """[T]: how far the last chosen logit lies above the best one left out, in standard deviations of all the
+    logits (inf when every expert is chosen)."""
+    z = matmul(h, w_router, round_to)
+    s = z.sort(dim=-1, descending=True).values
+    if s.shape[1] <= top:
+        return torch.full((h.shape[0],), float("inf"), dtype=F64)
+    return (s[:, top - 1] - s[:, top]) / z.std()
+
+
+def routed_ff(h, W, p, mlp, round_to, margins=None):
+    """sum over a token's chosen experts of expert(weight * h); expert = down(silu(gate z) * (up z)).
+    margins, a list, receives this layer's `router_margin`."""
     n, top = int(mlp["router"]["experts"]), int(mlp["router"]["top"])
     idx, w = router_choice(h, W[p + "router"], top, round_to)
+    if margins is not None:
+        margins.append(router_margin(h, W[p + "router"], top, round_to))
     y = torch.zeros(h.shape[0], W[p + "e0.down"].shape[0], dtype=F64)
     for e in range(n):
         for j in range(top):
@@ -236,9 +249,9 @@ def streams_write(X, M, b, y):
 
 
 # --------------------------------------------------------------------------- the model
-def forward(cfg, W, tokens, round_to=None, layers_out=None):
+def forward(cfg, W, tokens, round_to=None, layers_out=None, margins=None):
     """Logits [T, vocab] (float64) of one sequence from position 0.  layers_out, a list, receives the
-    sum of the streams [T, E] after every layer."""
+    sum of the streams [T, E] after every layer; margins, a list, every routed layer's `router_margin`."""
     eps = float(cfg["norm"]["eps"])
     S = int(cfg.get("streams", 1))
     W = {k: (rnd(v, round_to) if v.dim() >= 2 else v) for k, v in W.items()}
@@ -261,7 +274,7 @@ def forward(cfg, W, tokens, round_to=None, layers_out=None):
         def ff(h):
             if L["mlp"]["kind"] == "dense":
                 return dense_ff(h, W, p + "mlp.", round_to)
-            return routed_ff(h, W, p + "mlp.", L["mlp"], round_to)
+            return routed_ff(h, W, p + "mlp.", L["mlp"], round_to, margins)
 
         subs = [(mixer, "1")] + ([(ff, "2")] if L.get("mlp") is not None else [])
         for f, q in subs:

@@ -212,6 +212,205 @@ moe_gemm_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, int w
   }
 }
 
+// ------------------------------------------------------------------ the grouped product on the tensor cores (16-bit types)
+// The same tiles of rows of one expert, on mma.sync m16n8k16 with float32 accumulators.  A CTA owns BM sorted rows and
+// 64 output features (in the gated form 64 gate rows and the 64 up rows that belong to them, two accumulators that the
+// epilogue combines).  K runs in blocks of 64 elements (128 bytes a row) through a ring of cp.async stages; rows are
+// stored with their 16-byte chunks XOR-swizzled by the row so that ldmatrix reads without bank conflicts.  Rows past the
+// group, features past N and chunks past K are filled with zeros by the copies and masked in the stores, so a row's
+// result is the K-ordered sum of its own products whatever shares its tile.  Needs K and lda multiples of 8 elements
+// and 16-byte aligned operands (the launcher checks; everything else takes the CUDA-core kernel above).
+namespace moe_mma {
+
+constexpr int BN = 64, BK = 64;
+
+__device__ __forceinline__ void cp16(void* smem, const void* gmem, int src_bytes) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(gmem), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void ldsm4(unsigned (&r)[4], const void* smem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+template <typename T>
+__device__ __forceinline__ void mma(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1);
+template <>
+__device__ __forceinline__ void mma<__half>(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <>
+__device__ __forceinline__ void mma<__nv_bfloat16>(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// element (row, col) of a [rows][64] 16-bit tile whose 16-byte chunks are XOR-swizzled by the row
+template <typename T>
+__device__ __forceinline__ T* at(T* base, int row, int col) {
+  return base + row * BK + ((((col >> 3) ^ (row & 7)) << 3) | (col & 7));
+}
+
+template <int BM, int STAGES, bool GLU>
+constexpr int smem_bytes() { return STAGES * (BM + (GLU ? 2 : 1) * BN) * BK * 2; }
+
+template <typename T, int BM, int WM, int WN, int STAGES, bool GLU>
+__global__ void __launch_bounds__(WM * WN * 32)
+kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, int w_rows, int K, int N, int n_exp,
+       const int* __restrict__ counts, int act, void* __restrict__ out, int ldo) {
+  constexpr int NT = WM * WN * 32;
+  constexpr int NB = GLU ? 2 : 1;
+  constexpr int MI = BM / WM / 16, NI = BN / WN / 8;
+  static_assert(MI >= 1 && NI >= 2 && NI % 2 == 0, "a warp needs 16 rows and 16 features at least");
+  constexpr int STAGE = (BM + NB * BN) * BK;      // elements
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  T* smem = reinterpret_cast<T*>(smem_raw);
+  __shared__ int tile_e, tile_row0, tile_rows;
+  if (threadIdx.x == 0) {
+    int left = blockIdx.x, first = 0, e = 0, rows = 0, row0 = 0;
+    for (; e < n_exp; ++e) {
+      const int c = counts[e];
+      const int tiles = (c + BM - 1) / BM;
+      if (left < tiles) {
+        row0 = first + left * BM;
+        rows = min(BM, first + c - row0);
+        break;
+      }
+      left -= tiles;
+      first += c;
+    }
+    tile_e = e;
+    tile_row0 = row0;
+    tile_rows = rows;          // 0: past the last tile
+  }
+  __syncthreads();
+  const int rows = tile_rows;
+  if (rows == 0) return;
+  const int row0 = tile_row0;
+  const int n0 = blockIdx.y * BN;
+  const T* We = W + (size_t)tile_e * w_rows * K;
+  const T* Ar = A + (size_t)row0 * lda;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int wm = warp / WN, wn = warp % WN;
+  const int nk = (K + BK - 1) / BK;
+
+  auto load = [&](int kb, int stage) {
+    T* sa = smem + stage * STAGE;
+    const int k0 = kb * BK;
+    for (int idx = threadIdx.x; idx < BM * 8; idx += NT) {
+      const int m = idx >> 3, c = idx & 7;
+      const bool in = m < rows && k0 + c * 8 < K;
+      cp16(at(sa, m, c * 8), in ? Ar + (size_t)m * lda + k0 + c * 8 : A, in ? 16 : 0);
+    }
+    T* sb = sa + BM * BK;
+    for (int idx = threadIdx.x; idx < NB * BN * 8; idx += NT) {
+      const int n = idx >> 3, c = idx & 7;          // n: 0..63 gate (or plain) rows, 64..127 up rows
+      const int f = n0 + (n & (BN - 1));
+      const bool in = f < N && k0 + c * 8 < K;
+      const size_t wr = (size_t)(n < BN ? f : N + f);
+      cp16(at(sb, n, c * 8), in ? We + wr * K + k0 + c * 8 : W, in ? 16 : 0);
+    }
+  };
+
+  float acc[NB][MI][NI][4];
+#pragma unroll
+  for (int g = 0; g < NB; ++g)
+#pragma unroll
+    for (int i = 0; i < MI; ++i)
+#pragma unroll
+      for (int j = 0; j < NI; ++j)
+#pragma unroll
+        for (int r = 0; r < 4; ++r) acc[g][i][j][r] = 0.f;
+
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) {
+    if (s < nk) load(s, s);
+    commit();
+  }
+  for (int kb = 0; kb < nk; ++kb) {
+    wait<STAGES - 2>();
+    __syncthreads();          // block kb has landed for everyone, and everyone is done with the stage refilled next
+    if (kb + STAGES - 1 < nk) load(kb + STAGES - 1, (kb + STAGES - 1) % STAGES);
+    commit();
+    const T* sa = smem + (kb % STAGES) * STAGE;
+    const T* sb = sa + BM * BK;
+#pragma unroll
+    for (int kk = 0; kk < BK; kk += 16) {
+      unsigned a[MI][4];
+#pragma unroll
+      for (int i = 0; i < MI; ++i)
+        ldsm4(a[i], at(sa, wm * (MI * 16) + i * 16 + (lane & 15), kk + (lane >> 4) * 8));
+#pragma unroll
+      for (int g = 0; g < NB; ++g)
+#pragma unroll
+        for (int j = 0; j < NI; j += 2) {
+          unsigned b[4];
+          ldsm4(b, at(sb, g * BN + wn * (NI * 8) + j * 8 + (lane & 7) + ((lane >> 4) << 3), kk + ((lane >> 3) & 1) * 8));
+#pragma unroll
+          for (int i = 0; i < MI; ++i) {
+            mma<T>(acc[g][i][j], a[i], b[0], b[1]);
+            mma<T>(acc[g][i][j + 1], a[i], b[2], b[3]);
+          }
+        }
+    }
+  }
+  wait<0>();
+#pragma unroll
+  for (int i = 0; i < MI; ++i)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int m = wm * (MI * 16) + i * 16 + (lane >> 2) + h * 8;
+      if (m >= rows) continue;
+      const size_t o = (size_t)(row0 + m) * ldo;
+#pragma unroll
+      for (int j = 0; j < NI; ++j)
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int n = n0 + wn * (NI * 8) + j * 8 + (lane & 3) * 2 + c;
+          if (n >= N) continue;
+          if (GLU) reinterpret_cast<T*>(out)[o + n] = from_f32<T>(moe_act(acc[0][i][j][h * 2 + c], act) * acc[NB - 1][i][j][h * 2 + c]);
+          else reinterpret_cast<float*>(out)[o + n] = acc[0][i][j][h * 2 + c];
+        }
+    }
+}
+
+template <typename T, int BM, int WM, int WN, int STAGES, bool GLU>
+int launch(const T* A, int lda, const T* W, int w_rows, int K, int N, int n_exp, const int* counts, int n_rows, int act, void* out,
+           int ldo, cudaStream_t stream) {
+  constexpr int smem = smem_bytes<BM, STAGES, GLU>();
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel<T, BM, WM, WN, STAGES, GLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    FERRUM_CHECK_ARG(e == cudaSuccess, "moe_gemm: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    configured = true;
+  }
+  const dim3 grid((n_rows + BM - 1) / BM + n_exp, (N + BN - 1) / BN);
+  kernel<T, BM, WM, WN, STAGES, GLU><<<grid, WM * WN * 32, smem, stream>>>(A, lda, W, w_rows, K, N, n_exp, counts, act, out, ldo);
+  FERRUM_CHECK_LAUNCH("moe_gemm (tensor cores)");
+  return 0;
+}
+
+template <typename T>
+int run(const void* A, int lda, const void* W, int w_rows, int K, int N, int n_exp, const int* counts, int n_rows, int glu, int act,
+        void* out, int ldo, cudaStream_t stream) {
+  const T* a = (const T*)A;
+  const T* w = (const T*)W;
+  const bool few = n_rows <= 32 * n_exp;        // about 32 rows an expert or fewer: tiles of 16 rows that stream the weights
+  if (few) {
+    if (glu) return launch<T, 16, 1, 4, 4, true>(a, lda, w, w_rows, K, N, n_exp, counts, n_rows, act, out, ldo, stream);
+    return launch<T, 16, 1, 4, 4, false>(a, lda, w, w_rows, K, N, n_exp, counts, n_rows, act, out, ldo, stream);
+  }
+  if (glu) return launch<T, 128, 4, 2, 3, true>(a, lda, w, w_rows, K, N, n_exp, counts, n_rows, act, out, ldo, stream);
+  return launch<T, 128, 4, 2, 3, false>(a, lda, w, w_rows, K, N, n_exp, counts, n_rows, act, out, ldo, stream);
+}
+
+}  // namespace moe_mma
+
 // y[t][:] = sum over the token's choices, in their order, of rows[row_of[t*top + j]][:] (float32), each times
 // weight_of[t*top + j] when that is given; for consumers that want a plain buffer.
 __global__ void __launch_bounds__(256)
@@ -226,6 +425,13 @@ moe_combine_kernel(const float* __restrict__ rows, int ld, const int* __restrict
     }
     y[(size_t)t * E + i] = s;
   }
+}
+
+static bool g_moe_cuda_cores = false;
+// Tests and measurements: 1 sends 16-bit products to the CUDA-core kernel too.
+FERRUM_API int ferrum_moe_cuda_cores(int on) {
+  g_moe_cuda_cores = on != 0;
+  return 0;
 }
 
 FERRUM_API int ferrum_moe_max_experts() { return MOE_MAX_EXPERTS; }
@@ -259,6 +465,12 @@ FERRUM_API int ferrum_moe_gemm(const void* A, int lda, const void* W, int w_rows
   if (n_rows == 0) return 0;
   const int ntile = (N + 63) / 64;
   FERRUM_CHECK_ARG(ntile <= 65535, "moe_gemm: too many output features");
+  if (dtype != FERRUM_F32 && !g_moe_cuda_cores && K % 8 == 0 && lda % 8 == 0 && (reinterpret_cast<uintptr_t>(A) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(W) & 15) == 0) {
+    if (dtype == FERRUM_BF16)
+      return moe_mma::run<__nv_bfloat16>(A, lda, W, w_rows, K, N, n_exp, counts, n_rows, glu, act, out, ldo, stream);
+    if (dtype == FERRUM_F16) return moe_mma::run<__half>(A, lda, W, w_rows, K, N, n_exp, counts, n_rows, glu, act, out, ldo, stream);
+  }
   if (n_rows <= 256) {
     const dim3 grid((n_rows + 15) / 16 + n_exp, ntile);
     FERRUM_DISPATCH_DTYPE(dtype, T, (moe_gemm_kernel<T, 16><<<grid, 256, 0, stream>>>(

@@ -26,7 +26,7 @@ TC_STORE_BF16, TC_STORE_F32, TC_RESIDUAL, TC_SWIGLU = 0, 1, 2, 3       # tcgen05
 
 _lib = None
 _lock = threading.Lock()
-ABI = 13
+ABI = 14
 
 
 def lib():
@@ -999,6 +999,11 @@ def moe_gemm(a, w, counts, n_rows, out, N, glu=None):
     _check(lib().ferrum_moe_gemm(_ptr(a), c_int(a.stride(0)), _ptr(w), c_int(w_rows), c_int(K), c_int(N), c_int(n_exp), _ptr(counts),
                                  c_int(n_rows), dtype_code(a.dtype), c_int(1 if glu else 0), c_int(GLU_ACTS[glu] if glu else 0),
                                  _ptr(out), c_int(out.stride(0)), _stream()), "moe_gemm")
+
+
+def set_moe_cuda_cores(on: bool):
+    """Tests and measurements: send 16-bit grouped products to the CUDA-core kernel too."""
+    lib().ferrum_moe_cuda_cores(c_int(1 if on else 0))
 
 
 def moe_combine(rows, row_of, top, n_tokens, y, weight_of=None):

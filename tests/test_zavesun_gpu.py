@@ -359,10 +359,13 @@ def test_one_stream_with_ones_is_the_plain_residual_sum(cuda):
 # ================================================================= the routed feed-forward alone
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("E,F,n_exp,top,T", [(52, 20, 5, 2, 37), (128, 64, 4, 1, 300), (40, 24, 1, 1, 9), (64, 32, 16, 4, 70), (72, 100, 40, 8, 11),
-                                             (320, 96, 8, 1, 2)])
+                                             (320, 96, 8, 1, 2), (200, 88, 3, 2, 700), (264, 168, 6, 1, 150)])
 def test_routed_feed_forward_alone(cuda, dtype, E, F, n_exp, top, T):
     """Router, choice, gather, both grouped products and the sum against the plain function; with more
-    experts than tokens some experts get no row, with one expert all rows are its."""
+    experts than tokens some experts get no row, with one expert all rows are its.  In bfloat16 the sizes
+    that are multiples of 8 take the tensor-core product (few rows an expert: tiles of 16 rows; many: of
+    128, several per expert, with ragged last tiles and feature counts that end inside a tile), the others
+    the CUDA-core one."""
     from ferrum_b200.parts import RoutedFeedForward
     td = TD[dtype]
     ff = RoutedFeedForward(E, F, n_exp, top, td)
@@ -383,6 +386,17 @@ def test_routed_feed_forward_alone(cuda, dtype, E, F, n_exp, top, T):
     err = (y[:T].double().cpu() - ref)[sure].abs().max()
     assert err < (2e-5 if dtype == "float32" else 3e-2) * ref.abs().max(), err
     assert torch.equal(y[T], torch.full((E,), 7.0, device="cuda"))
+    if dtype != "float32":
+        # both kernels of the grouped product see the same 16-bit operands and sum in float32: they agree far closer
+        # than either does with the plain function (an activation may round the other way now and then)
+        from ferrum_b200.ops import lib as ops
+        y2 = torch.zeros(T, E, device="cuda")
+        ops.set_moe_cuda_cores(True)
+        try:
+            ff.forward(x, ctx, y2, accumulate=False)
+        finally:
+            ops.set_moe_cuda_cores(False)
+        assert (y2 - y[:T]).abs().max() < 4e-3 * ref.abs().max()
 
 
 def test_router_prefers_the_lower_index_in_a_tie_and_counts_rows(cuda):

@@ -11,6 +11,8 @@ peaks.  This is the small case that `ncu` captures are taken on.
     python kernel_bench.py head_linear --tokens 8 --hq 16 --n 512 --k 128
     python kernel_bench.py attn_decode|attn_prefill --exact [--window W] [--penalty]   (float32 weights and sums on 16-bit storage)
     python kernel_bench.py ssm --tokens 2048 [--batch 1] [--hq 64] [--head-dim 64] [--state 128]   (the state-space mixer's kernels)
+    python kernel_bench.py moe --tokens 4096 --n 2816 --k 2048 [--experts 8] [--epilogue store|swiglu] [--cuda-cores]   (grouped product of a routed feed-forward)
+    python kernel_bench.py streams --tokens 2048 --k 2048 [--hq 4]   (write, read and norm over --hq residual streams)
     python kernel_bench.py rmsnorm|rope --tokens 8
     python kernel_bench.py step --tokens 2048 [--layers 2] [--dtype bf16|fp16|fp32]   (one prompt portion through the model)
     FERRUM_KERNEL_TRACE=1 python kernel_bench.py timeline [--batch 8] [--context 8192] [--layers 4]
@@ -35,7 +37,7 @@ sys.path.insert(0, ROOT)
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["attn_decode", "attn_prefill", "latent_decode", "latent_prefill", "head_linear", "gemm", "rmsnorm",
+    ap.add_argument("kernel", choices=["attn_decode", "attn_prefill", "latent_decode", "latent_prefill", "head_linear", "gemm", "moe", "streams", "rmsnorm",
                                        "rope", "ssm", "step", "timeline"])
     ap.add_argument("--kv-rank", type=int, default=512, help="latent_*: elements of the cached latent (the values)")
     ap.add_argument("--rot-dim", type=int, default=64, help="latent_*: rotated key elements behind the latent")
@@ -44,6 +46,7 @@ def main():
     ap.add_argument("--cuda-cores", action="store_true", help="latent_*: the CUDA-core kernel also where the tensor-core one applies")
     ap.add_argument("--exact", action="store_true", help="attn_*: the CUDA-core kernel with float32 results, as the shaped attention runs it")
     ap.add_argument("--penalty", action="store_true", help="attn_* --exact: with a distance penalty per head")
+    ap.add_argument("--experts", type=int, default=8, help="moe: experts that share the rows")
     ap.add_argument("--state", type=int, default=128, help="ssm: state elements per head and value element")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
@@ -210,6 +213,29 @@ def main():
         wb = N * K * esize * (2 if dual else 1)
         work = {"bytes": wb + M * K * esize + M * N * (4 if args.epilogue == "residual" else esize),
                 "flops": 2.0 * M * N * K * (2 if dual else 1), "bound": "hbm" if M <= 128 else "tensor"}
+    elif args.kernel == "moe":
+        # --tokens sorted rows spread evenly over the experts (the last takes the remainder); swiglu: gate and up rows and the activation
+        R, N, K, X = args.tokens, args.n, args.k, args.experts
+        glu = args.epilogue == "swiglu"
+        share = [R // X] * X
+        share[-1] += R - sum(share)
+        counts = torch.tensor(share, dtype=torch.int32, device=dev)
+        a = torch.randn(R, K, device=dev, generator=gen).to(td)
+        weights = [torch.randn(X, N * (2 if glu else 1), K, device=dev, generator=gen).mul_(0.02).to(td) for _ in range(args.copies)]
+        o = torch.empty(R, N, device=dev, dtype=td if glu else torch.float32)
+        ops.set_moe_cuda_cores(args.cuda_cores)
+        runs = [lambda w=w: ops.moe_gemm(a, w, counts, R, o, N, glu="silu" if glu else None) for w in weights]
+        work = {"bytes": weights[0].numel() * esize + R * K * esize + o.numel() * o.element_size(),
+                "flops": 2.0 * R * N * K * (2 if glu else 1), "bound": "hbm" if R <= 32 * X else "tensor"}
+    elif args.kernel == "streams":
+        T, E, S = args.tokens, args.k, args.hq
+        Xs = [torch.randn(T, S * E, device=dev, generator=gen) for _ in range(args.copies)]
+        y = torch.randn(T, E, device=dev, generator=gen)
+        mix, ow, iw = torch.eye(S, device=dev), torch.ones(S, device=dev), torch.full((S,), 1.0 / S, device=dev)
+        w = torch.ones(E, device=dev)
+        o = torch.empty(T, E, device=dev, dtype=td)
+        runs = [lambda X=X: ops.hyper_step(X, S, E, T, write=ops.StreamWrite(mix, ow, y=y), in_w=iw, norm_w=w, eps=1e-6, out=o) for X in Xs]
+        work = {"bytes": T * E * (8 * S + 4 + esize), "flops": 0.0, "bound": "hbm"}
     elif args.kernel == "rmsnorm":
         T, E = args.tokens, args.k
         x = torch.randn(T, E, device=dev, generator=gen)

@@ -214,7 +214,7 @@ moe_gemm_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, int w
 
 // ------------------------------------------------------------------ the grouped product on the tensor cores (16-bit types)
 // The same tiles of rows of one expert, on mma.sync m16n8k16 with float32 accumulators.  A CTA owns BM sorted rows and
-// 64 output features (in the gated form 64 gate rows and the 64 up rows that belong to them, two accumulators that the
+// BN output features (in the gated form BN gate rows and the BN up rows that belong to them, two accumulators that the
 // epilogue combines).  K runs in blocks of 64 elements (128 bytes a row) through a ring of cp.async stages; rows are
 // stored with their 16-byte chunks XOR-swizzled by the row so that ldmatrix reads without bank conflicts.  Rows past the
 // group, features past N and chunks past K are filled with zeros by the copies and masked in the stores, so a row's
@@ -222,7 +222,7 @@ moe_gemm_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, int w
 // and 16-byte aligned operands (the launcher checks; everything else takes the CUDA-core kernel above).
 namespace moe_mma {
 
-constexpr int BN = 64, BK = 64;
+constexpr int BK = 64;
 
 __device__ __forceinline__ void cp16(void* smem, const void* gmem, int src_bytes) {
   const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -256,13 +256,13 @@ __device__ __forceinline__ T* at(T* base, int row, int col) {
   return base + row * BK + ((((col >> 3) ^ (row & 7)) << 3) | (col & 7));
 }
 
-template <int BM, int STAGES, bool GLU>
+template <int BM, int BN, int STAGES, bool GLU>
 constexpr int smem_bytes() { return STAGES * (BM + (GLU ? 2 : 1) * BN) * BK * 2; }
 
-template <typename T, int BM, int WM, int WN, int STAGES, bool GLU>
+template <typename T, int BM, int BN, int WM, int WN, int STAGES, bool GLU>
 __global__ void __launch_bounds__(WM * WN * 32)
-kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, int w_rows, int K, int N, int n_exp,
-       const int* __restrict__ counts, int act, void* __restrict__ out, int ldo) {
+moe_gemm_mma_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, int w_rows, int K, int N, int n_exp,
+                    const int* __restrict__ counts, int act, void* __restrict__ out, int ldo) {
   constexpr int NT = WM * WN * 32;
   constexpr int NB = GLU ? 2 : 1;
   constexpr int MI = BM / WM / 16, NI = BN / WN / 8;
@@ -299,23 +299,52 @@ kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, int w_rows, in
   const int wm = warp / WN, wn = warp % WN;
   const int nk = (K + BK - 1) / BK;
 
+  // Every thread copies the same 16-byte chunk column (c) of rows lr, lr + RS, lr + 2 RS, ... of both operands: the
+  // rows' pointers, their places in a stage and whether they exist are worked out once; a k-block costs an add and
+  // the copy per chunk.
+  constexpr int RS = NT / 8;                        // rows between two chunks of a thread (a multiple of 8)
+  constexpr int AI = BM / RS, BI = NB * BN / RS;    // chunks a thread copies per k-block
+  static_assert(BM % RS == 0 && BN % RS == 0 && RS % 8 == 0, "the copy plan needs whole rounds of the threads");
+  const int lr = threadIdx.x >> 3, c = threadIdx.x & 7, kc = c * 8;
+  const unsigned smem0 = (unsigned)__cvta_generic_to_shared(smem);
+  const unsigned dst0 = (unsigned)((lr * BK + ((c ^ (lr & 7)) << 3)) * 2);      // bytes; row lr + i RS lies i RS rows on
+  const T* pa[AI];
+  const T* pb[BI];
+  unsigned ok_a = 0, ok_b = 0;
+#pragma unroll
+  for (int i = 0; i < AI; ++i) {
+    const int m = lr + i * RS;
+    if (m < rows) ok_a |= 1u << i;
+    pa[i] = m < rows ? Ar + (size_t)m * lda + kc : A;
+  }
+#pragma unroll
+  for (int i = 0; i < BI; ++i) {
+    const int n = lr + i * RS;                      // 0..BN-1 gate (or plain) rows, then the up rows
+    const int f = n0 + (n & (BN - 1));
+    if (f < N) ok_b |= 1u << i;
+    pb[i] = f < N ? We + (size_t)(n < BN ? f : N + f) * K + kc : W;
+  }
   auto load = [&](int kb, int stage) {
-    T* sa = smem + stage * STAGE;
     const int k0 = kb * BK;
-    for (int idx = threadIdx.x; idx < BM * 8; idx += NT) {
-      const int m = idx >> 3, c = idx & 7;
-      const bool in = m < rows && k0 + c * 8 < K;
-      cp16(at(sa, m, c * 8), in ? Ar + (size_t)m * lda + k0 + c * 8 : A, in ? 16 : 0);
+    const bool kin = k0 + kc < K;
+    const unsigned sa = smem0 + (unsigned)(stage * STAGE * 2) + dst0;
+#pragma unroll
+    for (int i = 0; i < AI; ++i) {
+      const bool in = kin && ((ok_a >> i) & 1u);
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(sa + i * RS * BK * 2), "l"(in ? pa[i] + k0 : pa[i]), "r"(in ? 16 : 0) : "memory");
     }
-    T* sb = sa + BM * BK;
-    for (int idx = threadIdx.x; idx < NB * BN * 8; idx += NT) {
-      const int n = idx >> 3, c = idx & 7;          // n: 0..63 gate (or plain) rows, 64..127 up rows
-      const int f = n0 + (n & (BN - 1));
-      const bool in = f < N && k0 + c * 8 < K;
-      const size_t wr = (size_t)(n < BN ? f : N + f);
-      cp16(at(sb, n, c * 8), in ? We + wr * K + k0 + c * 8 : W, in ? 16 : 0);
+#pragma unroll
+    for (int i = 0; i < BI; ++i) {
+      const bool in = kin && ((ok_b >> i) & 1u);
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(sa + (BM + i * RS) * BK * 2), "l"(in ? pb[i] + k0 : pb[i]), "r"(in ? 16 : 0) : "memory");
     }
   };
+  // ldmatrix addresses: a lane's row is fixed, and its chunk in k-step kk is (kk / 8 + hi) ^ (row & 7) = (kk / 8) ^ t with
+  // t fixed (kk / 8 is even, hi is 0 or 1), so the byte offset within a stage is a fixed one XOR 2 kk.
+  const int row_a = wm * (MI * 16) + (lane & 15);
+  const unsigned off_a = (unsigned)(row_a * BK * 2 + ((((lane >> 4) ^ (row_a & 7)) & 7) << 4));
+  const int row_b = wn * (NI * 8) + (lane & 7) + ((lane >> 4) << 3);
+  const unsigned off_b = (unsigned)((BM + row_b) * BK * 2 + (((((lane >> 3) & 1) ^ (row_b & 7)) & 7) << 4));
 
   float acc[NB][MI][NI][4];
 #pragma unroll
@@ -337,20 +366,24 @@ kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, int w_rows, in
     __syncthreads();          // block kb has landed for everyone, and everyone is done with the stage refilled next
     if (kb + STAGES - 1 < nk) load(kb + STAGES - 1, (kb + STAGES - 1) % STAGES);
     commit();
-    const T* sa = smem + (kb % STAGES) * STAGE;
-    const T* sb = sa + BM * BK;
+    const unsigned st = smem0 + (unsigned)((kb % STAGES) * STAGE * 2);
 #pragma unroll
     for (int kk = 0; kk < BK; kk += 16) {
       unsigned a[MI][4];
 #pragma unroll
-      for (int i = 0; i < MI; ++i)
-        ldsm4(a[i], at(sa, wm * (MI * 16) + i * 16 + (lane & 15), kk + (lane >> 4) * 8));
+      for (int i = 0; i < MI; ++i) {
+        const unsigned ad = st + (off_a ^ (unsigned)(kk * 2)) + i * 16 * BK * 2;
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(a[i][0]), "=r"(a[i][1]), "=r"(a[i][2]), "=r"(a[i][3]) : "r"(ad));
+      }
 #pragma unroll
       for (int g = 0; g < NB; ++g)
 #pragma unroll
         for (int j = 0; j < NI; j += 2) {
           unsigned b[4];
-          ldsm4(b, at(sb, g * BN + wn * (NI * 8) + j * 8 + (lane & 7) + ((lane >> 4) << 3), kk + ((lane >> 3) & 1) * 8));
+          const unsigned ad = st + (off_b ^ (unsigned)(kk * 2)) + (g * BN + j * 8) * BK * 2;
+          asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                       : "=r"(b[0]), "=r"(b[1]), "=r"(b[2]), "=r"(b[3]) : "r"(ad));
 #pragma unroll
           for (int i = 0; i < MI; ++i) {
             mma<T>(acc[g][i][j], a[i], b[0], b[1]);
@@ -379,18 +412,18 @@ kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, int w_rows, in
     }
 }
 
-template <typename T, int BM, int WM, int WN, int STAGES, bool GLU>
+template <typename T, int BM, int BN, int WM, int WN, int STAGES, bool GLU>
 int launch(const T* A, int lda, const T* W, int w_rows, int K, int N, int n_exp, const int* counts, int n_rows, int act, void* out,
            int ldo, cudaStream_t stream) {
-  constexpr int smem = smem_bytes<BM, STAGES, GLU>();
+  constexpr int smem = smem_bytes<BM, BN, STAGES, GLU>();
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kernel<T, BM, WM, WN, STAGES, GLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(moe_gemm_mma_kernel<T, BM, BN, WM, WN, STAGES, GLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     FERRUM_CHECK_ARG(e == cudaSuccess, "moe_gemm: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
   const dim3 grid((n_rows + BM - 1) / BM + n_exp, (N + BN - 1) / BN);
-  kernel<T, BM, WM, WN, STAGES, GLU><<<grid, WM * WN * 32, smem, stream>>>(A, lda, W, w_rows, K, N, n_exp, counts, act, out, ldo);
+  moe_gemm_mma_kernel<T, BM, BN, WM, WN, STAGES, GLU><<<grid, WM * WN * 32, smem, stream>>>(A, lda, W, w_rows, K, N, n_exp, counts, act, out, ldo);
   FERRUM_CHECK_LAUNCH("moe_gemm (tensor cores)");
   return 0;
 }
@@ -402,11 +435,11 @@ int run(const void* A, int lda, const void* W, int w_rows, int K, int N, int n_e
   const T* w = (const T*)W;
   const bool few = n_rows <= 32 * n_exp;        // about 32 rows an expert or fewer: tiles of 16 rows that stream the weights
   if (few) {
-    if (glu) return launch<T, 16, 1, 4, 4, true>(a, lda, w, w_rows, K, N, n_exp, counts, n_rows, act, out, ldo, stream);
-    return launch<T, 16, 1, 4, 4, false>(a, lda, w, w_rows, K, N, n_exp, counts, n_rows, act, out, ldo, stream);
+    if (glu) return launch<T, 16, 64, 1, 4, 4, true>(a, lda, w, w_rows, K, N, n_exp, counts, n_rows, act, out, ldo, stream);
+    return launch<T, 16, 64, 1, 4, 4, false>(a, lda, w, w_rows, K, N, n_exp, counts, n_rows, act, out, ldo, stream);
   }
-  if (glu) return launch<T, 128, 4, 2, 3, true>(a, lda, w, w_rows, K, N, n_exp, counts, n_rows, act, out, ldo, stream);
-  return launch<T, 128, 4, 2, 3, false>(a, lda, w, w_rows, K, N, n_exp, counts, n_rows, act, out, ldo, stream);
+  if (glu) return launch<T, 128, 64, 4, 2, 3, true>(a, lda, w, w_rows, K, N, n_exp, counts, n_rows, act, out, ldo, stream);
+  return launch<T, 128, 128, 4, 2, 3, false>(a, lda, w, w_rows, K, N, n_exp, counts, n_rows, act, out, ldo, stream);
 }
 
 }  // namespace moe_mma

@@ -12,7 +12,7 @@ peaks.  This is the small case that `ncu` captures are taken on.
     python kernel_bench.py attn_decode|attn_prefill --exact [--window W] [--penalty]   (float32 weights and sums on 16-bit storage)
     python kernel_bench.py ssm --tokens 2048 [--batch 1] [--hq 64] [--head-dim 64] [--state 128]   (the state-space mixer's kernels)
     python kernel_bench.py moe --tokens 4096 --n 2816 --k 2048 [--experts 8] [--epilogue store|swiglu] [--cuda-cores]   (grouped product of a routed feed-forward)
-    python kernel_bench.py streams --tokens 2048 --k 2048 [--hq 4]   (write, read and norm over --hq residual streams)
+    python kernel_bench.py streams --tokens 2048 --k 2048 [--streams 4]   (write, read and norm over the residual streams)
     python kernel_bench.py rmsnorm|rope --tokens 8
     python kernel_bench.py step --tokens 2048 [--layers 2] [--dtype bf16|fp16|fp32]   (one prompt portion through the model)
     FERRUM_KERNEL_TRACE=1 python kernel_bench.py timeline [--batch 8] [--context 8192] [--layers 4]
@@ -46,6 +46,7 @@ def main():
     ap.add_argument("--cuda-cores", action="store_true", help="latent_*: the CUDA-core kernel also where the tensor-core one applies")
     ap.add_argument("--exact", action="store_true", help="attn_*: the CUDA-core kernel with float32 results, as the shaped attention runs it")
     ap.add_argument("--penalty", action="store_true", help="attn_* --exact: with a distance penalty per head")
+    ap.add_argument("--streams", type=int, default=4, help="streams: copies of the residual stream")
     ap.add_argument("--experts", type=int, default=8, help="moe: experts that share the rows")
     ap.add_argument("--state", type=int, default=128, help="ssm: state elements per head and value element")
     ap.add_argument("--batch", type=int, default=8)
@@ -228,7 +229,7 @@ def main():
         work = {"bytes": weights[0].numel() * esize + R * K * esize + o.numel() * o.element_size(),
                 "flops": 2.0 * R * N * K * (2 if glu else 1), "bound": "hbm" if R <= 32 * X else "tensor"}
     elif args.kernel == "streams":
-        T, E, S = args.tokens, args.k, args.hq
+        T, E, S = args.tokens, args.k, args.streams
         Xs = [torch.randn(T, S * E, device=dev, generator=gen) for _ in range(args.copies)]
         y = torch.randn(T, E, device=dev, generator=gen)
         mix, ow, iw = torch.eye(S, device=dev), torch.ones(S, device=dev), torch.full((S,), 1.0 / S, device=dev)

@@ -10,8 +10,12 @@
 //             of rows of ONE expert (it finds expert and rows from the counters, so nothing about the
 //             routing passes through the host) and a tile of output features.  Two epilogues: the
 //             gated activation act(gate) * up from weight rows n and F + n, stored in the compute type;
-//             or float32 rows.  float32 accumulation in K order: a row's result does not depend on the
-//             rows it shares a tile with.
+//             or float32 rows.  float32 accumulation in an order that depends on K and on the kernel
+//             only: a row's result does not depend on the rows it shares a tile with.  Three kernels:
+//             tiles on the CUDA cores (float32, and 16-bit rows that are no 16-byte multiples), a
+//             warp per feature when an expert has a few rows (the same types, decoding), and tiles on
+//             the tensor cores for 16-bit types.  Which one runs depends on the step's row count, so a
+//             token's result in a small and in a large batch agrees to rounding, not bitwise.
 // The consumer adds a token's `top` result rows in the order of its choices (hyper.cu, or moe_combine,
 // which can multiply each by its choice's weight for designs that scale the expert's OUTPUT).
 #include "common.cuh"
@@ -209,6 +213,96 @@ moe_gemm_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, int w
       if (glu) reinterpret_cast<T*>(out)[row * ldo + n] = from_f32<T>(moe_act(acc[0][i][j], act) * acc[1][i][j]);
       else reinterpret_cast<float*>(out)[row * ldo + n] = acc[0][i][j];
     }
+  }
+}
+
+// ------------------------------------------------------------------ the grouped product for a few rows an expert (CUDA cores)
+// Decoding: an expert sees a handful of rows and the product is a stream of its weights.  A CTA owns up to 16 sorted
+// rows of one expert and 8 output features, one per warp (in the gated form the gate row and its up row); a lane walks
+// its elements of K (four consecutive ones of every 128 when rows are float32 on 16-byte boundaries, else every 32nd),
+// keeps one float32 sum per row, and the 32 lanes meet in a fixed shuffle tree.  The order of a row's sum is a function
+// of K alone.  The rows' elements are read through L1 by all eight warps.
+constexpr int MS_ROWS = 16, MS_WARPS = 8;
+
+template <typename T, bool GLU, bool VEC>
+__global__ void __launch_bounds__(MS_WARPS * 32)
+moe_gemm_skinny_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, int w_rows, int K, int N, int n_exp,
+                       const int* __restrict__ counts, int act, void* __restrict__ out, int ldo) {
+  __shared__ int tile_e, tile_row0, tile_rows;
+  if (threadIdx.x == 0) {
+    int left = blockIdx.x, first = 0, e = 0, rows = 0, row0 = 0;
+    for (; e < n_exp; ++e) {
+      const int c = counts[e];
+      const int tiles = (c + MS_ROWS - 1) / MS_ROWS;
+      if (left < tiles) {
+        row0 = first + left * MS_ROWS;
+        rows = min(MS_ROWS, first + c - row0);
+        break;
+      }
+      left -= tiles;
+      first += c;
+    }
+    tile_e = e;
+    tile_row0 = row0;
+    tile_rows = rows;          // 0: past the last tile
+  }
+  __syncthreads();
+  const int rows = tile_rows;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.y * MS_WARPS + warp;
+  if (rows == 0 || n >= N) return;
+  const int row0 = tile_row0;
+  const T* w0 = W + ((size_t)tile_e * w_rows + n) * K;
+  const T* w1 = w0 + (size_t)N * K;              // the up row (gated form)
+  const T* Ar = A + (size_t)row0 * lda;
+  float acc0[MS_ROWS], acc1[MS_ROWS];
+#pragma unroll
+  for (int m = 0; m < MS_ROWS; ++m) acc0[m] = acc1[m] = 0.f;
+  if (VEC) {
+#pragma unroll 2
+    for (int k = lane * 4; k < K; k += 128) {
+      const float4 g = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(w0) + k);
+      float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (GLU) u = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(w1) + k);
+#pragma unroll
+      for (int m = 0; m < MS_ROWS; ++m) {
+        if (m < rows) {
+          const float4 a = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(Ar) + (size_t)m * lda + k);
+          acc0[m] = fmaf(a.x, g.x, fmaf(a.y, g.y, fmaf(a.z, g.z, fmaf(a.w, g.w, acc0[m]))));
+          if (GLU) acc1[m] = fmaf(a.x, u.x, fmaf(a.y, u.y, fmaf(a.z, u.z, fmaf(a.w, u.w, acc1[m]))));
+        }
+      }
+    }
+  } else {
+    for (int k = lane; k < K; k += 32) {
+      const float g = to_f32<T>(w0[k]);
+      const float u = GLU ? to_f32<T>(w1[k]) : 0.f;
+#pragma unroll
+      for (int m = 0; m < MS_ROWS; ++m) {
+        if (m < rows) {
+          const float a = to_f32<T>(Ar[(size_t)m * lda + k]);
+          acc0[m] = fmaf(a, g, acc0[m]);
+          if (GLU) acc1[m] = fmaf(a, u, acc1[m]);
+        }
+      }
+    }
+  }
+  float r0 = 0.f, r1 = 0.f;
+#pragma unroll
+  for (int m = 0; m < MS_ROWS; ++m) {
+    if (m < rows) {
+      const float s0 = warp_sum(acc0[m]);
+      const float s1 = GLU ? warp_sum(acc1[m]) : 0.f;
+      if (lane == m) {
+        r0 = s0;
+        r1 = s1;
+      }
+    }
+  }
+  if (lane < rows) {
+    const size_t o = (size_t)(row0 + lane) * ldo + n;
+    if (GLU) reinterpret_cast<T*>(out)[o] = from_f32<T>(moe_act(r0, act) * r1);
+    else reinterpret_cast<float*>(out)[o] = r0;
   }
 }
 
@@ -504,13 +598,34 @@ FERRUM_API int ferrum_moe_gemm(const void* A, int lda, const void* W, int w_rows
       return moe_mma::run<__nv_bfloat16>(A, lda, W, w_rows, K, N, n_exp, counts, n_rows, glu, act, out, ldo, stream);
     if (dtype == FERRUM_F16) return moe_mma::run<__half>(A, lda, W, w_rows, K, N, n_exp, counts, n_rows, glu, act, out, ldo, stream);
   }
-  if (n_rows <= 256) {
+  if (n_rows <= 32 * n_exp) {         // about 32 rows an expert or fewer: a stream of the weights
+    const dim3 grid((n_rows + MS_ROWS - 1) / MS_ROWS + n_exp, (N + MS_WARPS - 1) / MS_WARPS);
+    FERRUM_CHECK_ARG(grid.y <= 65535, "moe_gemm: too many output features");
+    const bool vec = dtype == FERRUM_F32 && K % 4 == 0 && lda % 4 == 0 && (reinterpret_cast<uintptr_t>(A) & 15) == 0 &&
+                     (reinterpret_cast<uintptr_t>(W) & 15) == 0;
+#define MS_LAUNCH(T, G, V)                                                                                                   \
+  moe_gemm_skinny_kernel<T, G, V><<<grid, MS_WARPS * 32, 0, stream>>>((const T*)A, lda, (const T*)W, w_rows, K, N, n_exp, counts, \
+                                                                      act, out, ldo)
+    if (vec) {
+      if (glu) MS_LAUNCH(float, true, true);
+      else MS_LAUNCH(float, false, true);
+    } else if (glu) {
+      FERRUM_DISPATCH_DTYPE(dtype, T, MS_LAUNCH(T, true, false));
+    } else {
+      FERRUM_DISPATCH_DTYPE(dtype, T, MS_LAUNCH(T, false, false));
+    }
+#undef MS_LAUNCH
+  } else if (n_rows <= 256) {
     const dim3 grid((n_rows + 15) / 16 + n_exp, ntile);
     FERRUM_DISPATCH_DTYPE(dtype, T, (moe_gemm_kernel<T, 16><<<grid, 256, 0, stream>>>(
         (const T*)A, lda, (const T*)W, w_rows, K, N, n_exp, counts, glu, act, out, ldo)));
-  } else {
+  } else if (n_rows <= 96 * n_exp) {
     const dim3 grid((n_rows + 63) / 64 + n_exp, ntile);
     FERRUM_DISPATCH_DTYPE(dtype, T, (moe_gemm_kernel<T, 64><<<grid, 256, 0, stream>>>(
+        (const T*)A, lda, (const T*)W, w_rows, K, N, n_exp, counts, glu, act, out, ldo)));
+  } else {                            // about a hundred rows an expert or more: 8 x 4 outputs a thread
+    const dim3 grid((n_rows + 127) / 128 + n_exp, ntile);
+    FERRUM_DISPATCH_DTYPE(dtype, T, (moe_gemm_kernel<T, 128><<<grid, 256, 0, stream>>>(
         (const T*)A, lda, (const T*)W, w_rows, K, N, n_exp, counts, glu, act, out, ldo)));
   }
   FERRUM_CHECK_LAUNCH("moe_gemm");

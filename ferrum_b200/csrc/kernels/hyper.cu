@@ -13,7 +13,8 @@
 // listed tokens only and stores nothing (the last read of a model: the plain sum of the streams of
 // the rows whose logits are wanted, a == null).
 //
-// One block per token; a thread walks elements e = tid, tid + 256, ...; u stays in shared memory
+// One block per token; a thread walks elements e = tid, tid + 256, ... (four consecutive ones at a time, with 16-byte
+// accesses, when the rows allow it and the kernel is built for the number of streams); u stays in shared memory
 // between the sum of squares and the scaling.  Sums over s run in ascending order, the block's
 // reduction tree is fixed: a token's result does not depend on the batch.
 #include "common.cuh"
@@ -31,12 +32,17 @@ struct HyperWrite {
   const float* out;        // [S]
 };
 
-template <typename TOut>
+// V: consecutive elements a thread handles at once (4: rows of X, y and out start on 16-byte boundaries and E is a
+// multiple of 4, so that a thread's loads are 16 bytes wide and S + 1 of them are in flight before the arithmetic).
+// SC: the number of streams when the kernel is built for one (its loops and registers are then exactly that many), else 0.
+template <typename TOut, int V, int SC>
 __global__ void __launch_bounds__(HC_THREADS)
-hyper_step_kernel(float* __restrict__ X, int S, int E, const int* __restrict__ rows, const HyperWrite w, const PartialLayout L,
+hyper_step_kernel(float* __restrict__ X, int S_any, int E, const int* __restrict__ rows, const HyperWrite w, const PartialLayout L,
                   int has_write, int store, const float* __restrict__ in_w, const float* __restrict__ norm_w, float eps,
                   TOut* __restrict__ out) {
-  extern __shared__ float hc_u[];                    // E floats
+  constexpr int SM = SC > 0 ? SC : HC_MAX_STREAMS;
+  const int S = SC > 0 ? SC : S_any;
+  extern __shared__ __align__(16) float hc_u[];      // E floats
   __shared__ float red[32];
   __shared__ float sm_mix[HC_MAX_STREAMS * HC_MAX_STREAMS], sm_out[HC_MAX_STREAMS], sm_in[HC_MAX_STREAMS];
   __shared__ PartialTable tab;
@@ -53,42 +59,77 @@ hyper_step_kernel(float* __restrict__ X, int S, int E, const int* __restrict__ r
   __syncthreads();
   float* xt = X + (size_t)t * S * E;
   float ss = 0.f;
-  for (int e = threadIdx.x; e < E; e += HC_THREADS) {
-    float x[HC_MAX_STREAMS];
+  for (int e = threadIdx.x * V; e < E; e += HC_THREADS * V) {
+    float x[SM][V];
 #pragma unroll
-    for (int s = 0; s < HC_MAX_STREAMS; ++s) x[s] = s < S ? xt[(size_t)s * E + e] : 0.f;
-    if (has_write) {
-      float y;
-      if (L.ws != nullptr) {
-        y = partial_sum(L, tab, t, e);
-      } else if (w.y_rows != nullptr) {
-        y = 0.f;
-        for (int j = 0; j < w.top; ++j) y += w.y[(size_t)w.y_rows[(size_t)t * w.top + j] * w.ldy + e];
+    for (int s = 0; s < SM; ++s) {
+      if (V == 4) {
+        const float4 v = s < S ? *reinterpret_cast<const float4*>(xt + (size_t)s * E + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+        x[s][0] = v.x; x[s][1] = v.y; x[s][2 % V] = v.z; x[s][3 % V] = v.w;
       } else {
-        y = w.y[(size_t)t * w.ldy + e];
+        x[s][0] = s < S ? xt[(size_t)s * E + e] : 0.f;
       }
-      float nx[HC_MAX_STREAMS];
+    }
+    if (has_write) {
+      float y[V];
+      if (L.ws != nullptr) {
 #pragma unroll
-      for (int d = 0; d < HC_MAX_STREAMS; ++d) {
-        float acc = 0.f;
+        for (int i = 0; i < V; ++i) y[i] = partial_sum(L, tab, t, e + i);
+      } else if (w.y_rows != nullptr) {
 #pragma unroll
-        for (int s = 0; s < HC_MAX_STREAMS; ++s)
-          if (s < S && d < S) acc = fmaf(sm_mix[s * S + d], x[s], acc);
-        nx[d] = d < S ? fmaf(sm_out[d], y, acc) : 0.f;
+        for (int i = 0; i < V; ++i) y[i] = 0.f;
+        for (int j = 0; j < w.top; ++j) {
+          const float* src = w.y + (size_t)w.y_rows[(size_t)t * w.top + j] * w.ldy + e;
+          if (V == 4) {
+            const float4 v = *reinterpret_cast<const float4*>(src);
+            y[0] += v.x; y[1 % V] += v.y; y[2 % V] += v.z; y[3 % V] += v.w;
+          } else {
+            y[0] += src[0];
+          }
+        }
+      } else {
+        const float* src = w.y + (size_t)t * w.ldy + e;
+        if (V == 4) {
+          const float4 v = *reinterpret_cast<const float4*>(src);
+          y[0] = v.x; y[1 % V] = v.y; y[2 % V] = v.z; y[3 % V] = v.w;
+        } else {
+          y[0] = src[0];
+        }
       }
 #pragma unroll
-      for (int s = 0; s < HC_MAX_STREAMS; ++s) {
-        x[s] = nx[s];
-        if (store && s < S) xt[(size_t)s * E + e] = nx[s];
+      for (int i = 0; i < V; ++i) {
+        float nx[SM];
+#pragma unroll
+        for (int d = 0; d < SM; ++d) {
+          float acc = 0.f;
+#pragma unroll
+          for (int s = 0; s < SM; ++s)
+            if (s < S && d < S) acc = fmaf(sm_mix[s * S + d], x[s][i], acc);
+          nx[d] = d < S ? fmaf(sm_out[d], y[i], acc) : 0.f;
+        }
+#pragma unroll
+        for (int s = 0; s < SM; ++s) x[s][i] = nx[s];
+      }
+      if (store) {
+#pragma unroll
+        for (int s = 0; s < SM; ++s) {
+          if (s < S) {
+            if (V == 4) *reinterpret_cast<float4*>(xt + (size_t)s * E + e) = make_float4(x[s][0], x[s][1 % V], x[s][2 % V], x[s][3 % V]);
+            else xt[(size_t)s * E + e] = x[s][0];
+          }
+        }
       }
     }
     if (out != nullptr) {
-      float u = 0.f;
 #pragma unroll
-      for (int s = 0; s < HC_MAX_STREAMS; ++s)
-        if (s < S) u = fmaf(sm_in[s], x[s], u);
-      hc_u[e] = u;
-      ss = fmaf(u, u, ss);
+      for (int i = 0; i < V; ++i) {
+        float u = 0.f;
+#pragma unroll
+        for (int s = 0; s < SM; ++s)
+          if (s < S) u = fmaf(sm_in[s], x[s][i], u);
+        hc_u[e + i] = u;
+        ss = fmaf(u, u, ss);
+      }
     }
   }
   if (out == nullptr) return;
@@ -126,21 +167,37 @@ FERRUM_API int ferrum_hyper_step(float* X, int S, int E, const int* rows, int n_
   const HyperWrite w{y, ldy, y_rows, top, mix, out_w};
   const size_t smem = out != nullptr ? (size_t)E * sizeof(float) : 0;
   FERRUM_CHECK_ARG(smem <= 200 * 1024, "hyper_step: a row of %d floats does not fit shared memory", E);
-#define HC_LAUNCH(T)                                                                                                     \
+#define HC_LAUNCH(T, V, SC)                                                                                                  \
   do {                                                                                                                   \
     if (smem > 48 * 1024) {                                                                                              \
       static size_t reserved = 0;                                                                                        \
       if (smem > reserved) {                                                                                             \
-        cudaError_t e = cudaFuncSetAttribute(hyper_step_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        cudaError_t e = cudaFuncSetAttribute(hyper_step_kernel<T, V, SC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         FERRUM_CHECK_ARG(e == cudaSuccess, "hyper_step: cannot reserve shared memory: %s", cudaGetErrorString(e));      \
         reserved = smem;                                                                                                 \
       }                                                                                                                  \
     }                                                                                                                    \
-    launch_kernel(hyper_step_kernel<T>, n_rows, HC_THREADS, smem, stream, X, S, E, rows, w, L, has_write, store, in_w,    \
+    launch_kernel(hyper_step_kernel<T, V, SC>, n_rows, HC_THREADS, smem, stream, X, S, E, rows, w, L, has_write, store, in_w, \
                   norm_w, eps, (T*)out);                                                                                 \
   } while (0)
-  if (out == nullptr) HC_LAUNCH(float);
-  else FERRUM_DISPATCH_DTYPE(out_dtype, T, HC_LAUNCH(T));
+  const bool wide = E % 4 == 0 && (reinterpret_cast<uintptr_t>(X) & 15) == 0 &&
+                    (y == nullptr || (ldy % 4 == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0));
+#define HC_LAUNCH_S(T, V)                              \
+  do {                                                 \
+    if (S == 1) HC_LAUNCH(T, V, 1);                    \
+    else if (S == 2) HC_LAUNCH(T, V, 2);               \
+    else if (S == 3) HC_LAUNCH(T, V, 3);               \
+    else if (S == 4) HC_LAUNCH(T, V, 4);               \
+    else HC_LAUNCH(T, 1, 0);                           \
+  } while (0)
+  if (wide) {
+    if (out == nullptr) HC_LAUNCH_S(float, 4);
+    else FERRUM_DISPATCH_DTYPE(out_dtype, T, HC_LAUNCH_S(T, 4));
+  } else {
+    if (out == nullptr) HC_LAUNCH(float, 1, 0);
+    else FERRUM_DISPATCH_DTYPE(out_dtype, T, HC_LAUNCH(T, 1, 0));
+  }
+#undef HC_LAUNCH_S
 #undef HC_LAUNCH
   FERRUM_CHECK_LAUNCH("hyper_step");
   return 0;

@@ -130,17 +130,26 @@ class ShapedAttention(PagedAttention):
                       self.eps, q, cache.plane, cache.page_stride, cache.page_size, Hq, Hkv, Dk, Dv, Dp, cache.writes,
                       bias=self.w_bias, q_norm=self.w_q_norm_weight if self.qk_norm else None,
                       k_norm=self.w_k_norm_weight if self.qk_norm else None, q_temp=self.q_temp, value_mix=mix)
-        o = ctx.buf("sattn_o", (cap, Hq * Dp), torch.float32)
         penalty = (self.w_r1, self.w_r2) if self.has_penalty else ((self.slopes, None) if self.slopes is not None else None)
-        self._generic(q, o, ctx, cache, table, penalty)
         out = ctx.buf("sattn_out", (cap, Hq * Dv), self.dtype)
-        off = Hq * Dk + Hkv * (Dk + Dv)
-        gate = proj[:, off:off + Hq * Dv] if self.has_gate else None
-        ops.attention_finish(o, T, ctx, vrot.cos_sin if vrot is not None else None, vrot.pairing if vrot is not None else 0,
-                             gate, out, Hq, Dv, Dp)
+        if Dp == Dv and vrot is None and not self.has_gate:
+            # nothing is left to do to the heads' results: the attention kernel rounds its float32 sums once into `out`
+            self._generic(q, out, ctx, cache, table, penalty)
+        else:
+            o = ctx.buf("sattn_o", (cap, Hq * Dp), torch.float32)
+            self._generic(q, o, ctx, cache, table, penalty)
+            self._finish(o, out, proj, ctx, vrot)
         if defer and not accumulate:
             part = linear_deferred(out, self.w_output_weight, ctx, T)
             if part is not None:
                 return part
         linear(out, self.w_output_weight, residual, RESIDUAL if accumulate else STORE_F32, ctx, M=T)
         return None
+
+    def _finish(self, o, out, proj, ctx, vrot):
+        """Turn back, gate, drop the padding past vdim and round once."""
+        T, Hq, Hkv, Dk, Dv, Dp = ctx.n_tokens, self.Hq, self.Hkv, self.Dk, self.Dv, self.D
+        off = Hq * Dk + Hkv * (Dk + Dv)
+        gate = proj[:, off:off + Hq * Dv] if self.has_gate else None
+        ops.attention_finish(o, T, ctx, vrot.cos_sin if vrot is not None else None, vrot.pairing if vrot is not None else 0,
+                             gate, out, Hq, Dv, Dp)

@@ -41,6 +41,7 @@ enum TcEpilogue : int {
   TC_STORE_F32 = 1,   // out f32  [M, ldo] = acc
   TC_RESIDUAL = 2,    // out f32  [M, ldo] += acc
   TC_SWIGLU = 3,      // out 16-bit [M, ldo] = silu(acc0) * acc1   (DUAL only)
+  TC_GEGLU = 4,       // the same with the tanh form of gelu on acc0 (an entry point's argument; the kernels see TC_SWIGLU and glu_act)
 };
 
 struct TcParams {
@@ -59,7 +60,14 @@ struct TcParams {
   int half;            // 0: operands and 16-bit outputs are bfloat16; 1: float16
   long long wait_cycles;  // limit of every mbarrier wait (0: the default of about a second); tests shorten it
   int drop_loads;      // test hook: the producer requests no tile at all, so that the waits for them run out
+  int glu_act;         // activation of the gate in the SwiGLU epilogues: 0 silu, 1 gelu (tanh form)
 };
+
+// act(gate) of the gated epilogues, float32.
+__device__ __forceinline__ float tc_glu_act(float g, int act) {
+  if (act == 1) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+  return g / (1.0f + __expf(-g));
+}
 
 constexpr int TILE_N = 128;  // weight rows per tile (the instruction's M)
 constexpr int TILE_K = 64;   // bfloat16 per row of a stage: 128 bytes, one swizzle span
@@ -121,7 +129,7 @@ __device__ __forceinline__ void tc_apply16(const TcParams& p, int t_base, int n,
       const bool half = p.half != 0;
 #pragma unroll
       for (int j = 0; j < 16; ++j)
-        if (j < valid) out[j * ld] = bits16(a0[j] / (1.0f + __expf(-a0[j])) * a1[j], half);
+        if (j < valid) out[j * ld] = bits16(tc_glu_act(a0[j], p.glu_act) * a1[j], half);
       break;
     }
   }
@@ -727,7 +735,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       for (int j = 0; j < 16; ++j) {
         const float theirs = __shfl_xor_sync(0xffffffffu, odd ? v[j] : v[16 + j], 1);
         const float g = odd ? theirs : v[j], up = odd ? v[16 + j] : theirs;
-        st[j * (TILE_N / 2)] = bits16(g / (1.0f + __expf(-g)) * up, half);
+        st[j * (TILE_N / 2)] = bits16(tc_glu_act(g, p.glu_act) * up, half);
       }
       stage_send(stage, &tmap_out, false, n0_cta >> 1, t0 + c0);
     };
@@ -938,8 +946,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
             if (p.gated) {  // four neighbouring rows are two (gate, up) pairs
 #pragma unroll
               for (int k = 0; k < 8; ++k) {
-                const uint32_t o2 = pack2_bits(acc[k].x / (1.0f + __expf(-acc[k].x)) * acc[k].y,
-                                               acc[k].z / (1.0f + __expf(-acc[k].z)) * acc[k].w, p.half != 0);
+                const uint32_t o2 = pack2_bits(tc_glu_act(acc[k].x, p.glu_act) * acc[k].y,
+                                               tc_glu_act(acc[k].z, p.glu_act) * acc[k].w, p.half != 0);
                 *reinterpret_cast<uint32_t*>((uint16_t*)stage + (cg + k) * (TILE_N / 2) + (q4 >> 1)) = o2;
               }
               stage_send(stage, &tmap_out, false, n0 >> 1, t0 + c0);
@@ -1193,6 +1201,8 @@ FERRUM_API int ferrum_gemm_tc(const void* x, const void* w, void* out, int dtype
   FERRUM_CHECK_ARG(((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0, "gemm_tc: operands must be 16-byte aligned");
   FERRUM_CHECK_ARG(ldx >= K && ldw >= K && ldo >= N, "gemm_tc: a row stride is shorter than its row");
   const bool dual = dual_offset > 0;
+  const int glu_act = epilogue == TC_GEGLU ? 1 : 0;
+  if (epilogue == TC_GEGLU) epilogue = TC_SWIGLU;
   FERRUM_CHECK_ARG(dual == (epilogue == TC_SWIGLU), "gemm_tc: the SwiGLU epilogue needs dual_offset, and only it does");
   FERRUM_CHECK_ARG(epilogue >= 0 && epilogue <= 3, "gemm_tc: unknown epilogue %d", epilogue);
   FERRUM_CHECK_ARG(w_rows >= N + dual_offset, "gemm_tc: w has %d rows, needs %d", w_rows, N + dual_offset);
@@ -1212,6 +1222,7 @@ FERRUM_API int ferrum_gemm_tc(const void* x, const void* w, void* out, int dtype
   p.wait_cycles = g_wait_cycles;
   p.drop_loads = g_drop_loads;
   p.stream_weights = (M + bt - 1) / bt == 1;  // one token tile: no weight tile is read twice
+  p.glu_act = glu_act;
   CUtensorMap mw, mx;
   if (dual && M > TILE_N && g_pair_kernel && n_ctas >= 2 && ((uintptr_t)out & 15) == 0 && ldo % 8 == 0) {
     // Two products of many tokens: the pair kernel computes them as one product whose weight

@@ -22,11 +22,11 @@ _DT = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
 SIXTEEN_BIT = (torch.bfloat16, torch.float16)       # the tensor-core kernels take either
 
 EPI_STORE, EPI_STORE_F32, EPI_RESIDUAL = 0, 1, 2                       # generic product
-TC_STORE_BF16, TC_STORE_F32, TC_RESIDUAL, TC_SWIGLU = 0, 1, 2, 3       # tcgen05 product
+TC_STORE_BF16, TC_STORE_F32, TC_RESIDUAL, TC_SWIGLU, TC_GEGLU = 0, 1, 2, 3, 4       # tcgen05 product (GEGLU: SWIGLU with gelu_tanh on the gate)
 
 _lib = None
 _lock = threading.Lock()
-ABI = 14
+ABI = 15
 
 
 def lib():
@@ -354,7 +354,7 @@ def gemm_tc(x, w, out, epilogue, err, workspace, counters, M=None, N=None, dual_
     N = (w.shape[0] - dual_offset) if N is None else N
     if x.shape[1] != K or out.shape[1] < N or out.shape[0] < M or x.shape[0] < M:
         raise KernelError(f"gemm_tc: shapes do not agree: x {tuple(x.shape)} w {tuple(w.shape)} out {tuple(out.shape)}")
-    want = x.dtype if epilogue in (TC_STORE_BF16, TC_SWIGLU) else torch.float32
+    want = x.dtype if epilogue in (TC_STORE_BF16, TC_SWIGLU, TC_GEGLU) else torch.float32
     if out.dtype != want:
         raise KernelError(f"gemm_tc: out must be {want} for epilogue {epilogue}")
     _need(workspace, torch.float32, "workspace")

@@ -9,8 +9,8 @@ crates/model/src/weights.rs:165-167): gate and up then leave their product in fl
 kernel adds the biases and applies the activation, and the down bias is either added by a block
 that sums the sublayer's result itself (`accumulate=False`; it reads `down_bias`) or, when the
 part adds into the residual stream, is not supported.  `act` names the activation of the gate
-("silu" or "gelu_tanh"); another activation than silu takes the same float32 gate/up path, with or
-without biases.  `extra_rows` appends further weight rows to the gate/up matrix: a
+("silu" or "gelu_tanh"); gelu_tanh without biases has its own epilogue of the tensor-core product
+too, and elsewhere (a few tokens, rows the tensor cores refuse) takes the float32 gate/up path.  `extra_rows` appends further weight rows to the gate/up matrix: a
 block that needs another product of the same input gets it from the same launch
 (`forward(..., extra_out=...)` returns a view of those columns).
 """
@@ -75,6 +75,8 @@ class SwiGLU(FeedForward):
             if part is not None:
                 self.extra_out = ctx.buf("ffn_extra", (ctx.token_capacity, n - 2 * F), torch.float32) if n > 2 * F else None
                 ops.bias_glu_reduce(part, self.w_gate_bias, self.w_up_bias, act, T, F, self.act, extra=self.extra_out)
+            elif not self.bias and n == 2 * F and self.act == "gelu_tanh" and ops.gemm_tc_supported(x, self.w_gate_up):
+                linear_swiglu(x, self.w_gate_up, act, F, ctx, M=T, kind=self.act)      # the activation in the product's epilogue
             else:
                 gu = ctx.buf("ffn_gate_up_f32", (ctx.token_capacity, n), torch.float32)
                 linear(x, self.w_gate_up, gu, STORE_F32, ctx, M=T)

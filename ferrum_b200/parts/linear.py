@@ -49,14 +49,15 @@ def linear(x, w, out, mode, ctx, M=None):
         ops.gemm_generic(x, w, out, _GENERIC[mode], M=M)
 
 
-def linear_swiglu(x, w_gate_up, act, F, ctx, M=None):
-    """act = silu(x @ w_gate_up[:F].T) * (x @ w_gate_up[F:].T) in one kernel.  The caller
-    checks `ops.gemm_tc_supported` first."""
+def linear_swiglu(x, w_gate_up, act, F, ctx, M=None, kind="silu"):
+    """act = silu(x @ w_gate_up[:F].T) * (x @ w_gate_up[F:].T) in one kernel (kind="gelu_tanh": that
+    activation on the gate instead; always the product's own epilogue, never left in partials).  The
+    caller checks `ops.gemm_tc_supported` first."""
     M = x.shape[0] if M is None else M
     if M == 0:
         return
     K = w_gate_up.shape[1]
-    part = linear_deferred(x, w_gate_up, ctx, M, N=F, dual_offset=F) if ctx.defer_swiglu else None
+    part = linear_deferred(x, w_gate_up, ctx, M, N=F, dual_offset=F) if ctx.defer_swiglu and kind == "silu" else None
     if part is not None:
         ops.swiglu_reduce(act, M, F, part)
         return
@@ -64,4 +65,4 @@ def linear_swiglu(x, w_gate_up, act, F, ctx, M=None):
     # (with many tokens the library runs both products as one on its CTA-pair kernel, gate and
     # up rows interleaved, and applies the activation in that kernel's epilogue)
     ws, cnt = ctx.gemm_scratch(M, F, K, True)
-    ops.gemm_tc(x, w_gate_up, act, ops.TC_SWIGLU, ctx.err, ws, cnt, M=M, N=F, dual_offset=F)
+    ops.gemm_tc(x, w_gate_up, act, ops.TC_SWIGLU if kind == "silu" else ops.TC_GEGLU, ctx.err, ws, cnt, M=M, N=F, dual_offset=F)

@@ -399,6 +399,27 @@ def test_routed_feed_forward_alone(cuda, dtype, E, F, n_exp, top, T):
         assert (y2 - y[:T]).abs().max() < 4e-3 * ref.abs().max()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("E,F,T", [(52, 60, 9), (128, 256, 5), (128, 256, 300), (320, 384, 70), (256, 136, 1000)])
+def test_dense_feed_forward_with_gelu_alone(cuda, dtype, E, F, T):
+    """down(gelu_tanh(gate x) * up x) against the plain function: a few tokens (products left in partials, the
+    activation in the kernel that sums them), many tokens of tensor-core sizes (the activation in the product's own
+    epilogue, one CTA a tile and two), and sizes or a type the tensor cores do not take."""
+    from ferrum_b200.parts import SwiGLU
+    td = TD[dtype]
+    ff = SwiGLU(E, F, td, act="gelu_tanh")
+    w = fill_part(ff, 31, td, "p.")
+    x = torch.randn(T, E, device="cuda", generator=torch.Generator(device="cuda").manual_seed(32)).to(td)
+    ctx = make_ctx([(0, T)])
+    y = torch.full((T + 1, E), 7.0, device="cuda")
+    part = ff.forward(x, ctx, y, accumulate=False)
+    assert part is None and ctx.err.item() == 0
+    ref = P.dense_ff(x.double().cpu(), w, "p.", rounding_of(dtype))
+    err = (y[:T].double().cpu() - ref).abs().max()
+    assert err < (2e-5 if dtype == "float32" else 2e-2) * ref.abs().max(), err
+    assert torch.equal(y[T], torch.full((E,), 7.0, device="cuda"))
+
+
 def test_router_prefers_the_lower_index_in_a_tie_and_counts_rows(cuda):
     from ferrum_b200.ops import lib as ops
     T, n, top, E = 6, 5, 2, 8

@@ -126,13 +126,13 @@ __device__ __forceinline__ float moe_act(float z, int act) {
   return z / (1.f + expf(-z));
 }
 
-// A [rows][lda]; W [n_exp][w_rows][K]; counts [n_exp].  glu: out[row][n] = act(C[row][n]) * C[row][F + n] in T (N = F);
+// A [rows][lda]; W [n_exp][w_rows][K]; counts [n_exp].  GLU: out[row][n] = act(C[row][n]) * C[row][F + n] in T (N = F);
 // else out[row][n] = C[row][n] in float32.  BM x BN outputs per CTA, K in steps of BK
 // through shared memory, TM x TN outputs a thread.
-template <typename T, int BM>
+template <typename T, int BM, bool GLU>
 __global__ void __launch_bounds__(256)
 moe_gemm_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, int w_rows, int K, int N, int n_exp,
-                const int* __restrict__ counts, int glu, int act, void* __restrict__ out, int ldo) {
+                const int* __restrict__ counts, int act, void* __restrict__ out, int ldo) {
   constexpr int BN = 64, BK = 16;
   constexpr int TM = BM / 16, TN = 4;             // 16 x 16 threads
   __shared__ float sa[BK][BM + 1];
@@ -178,7 +178,7 @@ moe_gemm_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, int w
       const int n = idx / BK, k = idx % BK;
       const bool in = n0 + n < N && k0 + k < K;
       sb[0][k][n] = in ? to_f32<T>(We[(size_t)(n0 + n) * K + k0 + k]) : 0.f;
-      if (glu) sb[1][k][n] = in ? to_f32<T>(We[(size_t)(N + n0 + n) * K + k0 + k]) : 0.f;
+      if (GLU) sb[1][k][n] = in ? to_f32<T>(We[(size_t)(N + n0 + n) * K + k0 + k]) : 0.f;
     }
     __syncthreads();
 #pragma unroll
@@ -189,14 +189,14 @@ moe_gemm_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, int w
 #pragma unroll
       for (int j = 0; j < TN; ++j) {
         b0[j] = sb[0][k][tx * TN + j];
-        b1[j] = glu ? sb[1][k][tx * TN + j] : 0.f;
+        b1[j] = GLU ? sb[1][k][tx * TN + j] : 0.f;
       }
 #pragma unroll
       for (int i = 0; i < TM; ++i)
 #pragma unroll
         for (int j = 0; j < TN; ++j) {
           acc[0][i][j] = fmaf(a[i], b0[j], acc[0][i][j]);
-          if (glu) acc[1][i][j] = fmaf(a[i], b1[j], acc[1][i][j]);
+          if (GLU) acc[1][i][j] = fmaf(a[i], b1[j], acc[1][i][j]);
         }
     }
     __syncthreads();
@@ -210,7 +210,7 @@ moe_gemm_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, int w
     for (int j = 0; j < TN; ++j) {
       const int n = n0 + tx * TN + j;
       if (n >= N) continue;
-      if (glu) reinterpret_cast<T*>(out)[row * ldo + n] = from_f32<T>(moe_act(acc[0][i][j], act) * acc[1][i][j]);
+      if (GLU) reinterpret_cast<T*>(out)[row * ldo + n] = from_f32<T>(moe_act(acc[0][i][j], act) * acc[1][i][j]);
       else reinterpret_cast<float*>(out)[row * ldo + n] = acc[0][i][j];
     }
   }
@@ -598,6 +598,13 @@ FERRUM_API int ferrum_moe_gemm(const void* A, int lda, const void* W, int w_rows
       return moe_mma::run<__nv_bfloat16>(A, lda, W, w_rows, K, N, n_exp, counts, n_rows, glu, act, out, ldo, stream);
     if (dtype == FERRUM_F16) return moe_mma::run<__half>(A, lda, W, w_rows, K, N, n_exp, counts, n_rows, glu, act, out, ldo, stream);
   }
+#define MT_LAUNCH(BM)                                                                                                  \
+  do {                                                                                                                 \
+    if (glu) FERRUM_DISPATCH_DTYPE(dtype, T, (moe_gemm_kernel<T, BM, true><<<grid, 256, 0, stream>>>(                   \
+        (const T*)A, lda, (const T*)W, w_rows, K, N, n_exp, counts, act, out, ldo)));                                  \
+    else FERRUM_DISPATCH_DTYPE(dtype, T, (moe_gemm_kernel<T, BM, false><<<grid, 256, 0, stream>>>(                      \
+        (const T*)A, lda, (const T*)W, w_rows, K, N, n_exp, counts, act, out, ldo)));                                  \
+  } while (0)
   if (n_rows <= 32 * n_exp) {         // about 32 rows an expert or fewer: a stream of the weights
     const dim3 grid((n_rows + MS_ROWS - 1) / MS_ROWS + n_exp, (N + MS_WARPS - 1) / MS_WARPS);
     FERRUM_CHECK_ARG(grid.y <= 65535, "moe_gemm: too many output features");
@@ -617,17 +624,15 @@ FERRUM_API int ferrum_moe_gemm(const void* A, int lda, const void* W, int w_rows
 #undef MS_LAUNCH
   } else if (n_rows <= 256) {
     const dim3 grid((n_rows + 15) / 16 + n_exp, ntile);
-    FERRUM_DISPATCH_DTYPE(dtype, T, (moe_gemm_kernel<T, 16><<<grid, 256, 0, stream>>>(
-        (const T*)A, lda, (const T*)W, w_rows, K, N, n_exp, counts, glu, act, out, ldo)));
-  } else if (n_rows <= 96 * n_exp) {
+    MT_LAUNCH(16);
+  } else if (n_rows <= 96 * n_exp || !glu) {
     const dim3 grid((n_rows + 63) / 64 + n_exp, ntile);
-    FERRUM_DISPATCH_DTYPE(dtype, T, (moe_gemm_kernel<T, 64><<<grid, 256, 0, stream>>>(
-        (const T*)A, lda, (const T*)W, w_rows, K, N, n_exp, counts, glu, act, out, ldo)));
-  } else {                            // about a hundred rows an expert or more: 8 x 4 outputs a thread
+    MT_LAUNCH(64);
+  } else {                            // the gated form with about a hundred rows an expert or more: 2 x 8 x 4 outputs a thread
     const dim3 grid((n_rows + 127) / 128 + n_exp, ntile);
-    FERRUM_DISPATCH_DTYPE(dtype, T, (moe_gemm_kernel<T, 128><<<grid, 256, 0, stream>>>(
-        (const T*)A, lda, (const T*)W, w_rows, K, N, n_exp, counts, glu, act, out, ldo)));
+    MT_LAUNCH(128);
   }
+#undef MT_LAUNCH
   FERRUM_CHECK_LAUNCH("moe_gemm");
   return 0;
 }

@@ -1462,4 +1462,261 @@ FERRUM_API int ferrum_gemm_tc_noalloc(const void* x, const void* w, void* out, i
   FERRUM_CHECK_ARG(false, "gemm_tc_noalloc: no kernel for token tile %d", bt);
 }
 
+// ------------------------------------------------------------------ the grouped product: rows sorted by expert
+// out[row, n] = sum_k x[row, k] * w[expert of row][n, k] over rows that lie sorted by expert (counts[e] rows each, on the
+// device): the products of a routed feed-forward over a prompt portion.  The same roles, stages and tiles as the kernel
+// above (128 weight rows on the instruction's M side, GR_BT rows on its N side, two accumulators in tensor memory), with
+// whole tiles only: a tile is GR_BT rows of ONE expert and 128 of its features, CTA c takes tiles c, c + P, ...  The
+// list of row tiles (expert, first row, rows) is made on the device from the counters when the kernel starts, so
+// nothing about the routing passes through the host.  The weights are one tensor [experts * w_rows, K]; a row tile's box
+// may reach past its group's last row (into the next expert's rows) and a feature tile's past the expert's last
+// feature: those columns and lanes are computed and never stored.  DUAL: the gate rows n and the up rows N + n of the
+// expert, out = act(gate) * up in the operands' type; else float32 rows.
+constexpr int GR_BT = 128;
+constexpr int GR_MAX_ROW_TILES = 1024;
+
+struct GroupedParams {
+  const int* counts;   // [n_exp] rows per expert
+  int n_exp, w_rows;   // weight rows per expert in the tensor
+};
+
+template <bool DUAL>
+__global__ void __launch_bounds__(192, 1)
+gemm_tc_grouped_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const TcParams p,
+                       const GroupedParams g) {
+  constexpr int BT = GR_BT;
+  using Cfg = TcConfig<BT, DUAL>;
+  constexpr int STAGES = Cfg::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = (uint64_t*)(smem + STAGES * Cfg::STAGE_BYTES);  // full[S], empty[S], acc_full[2], acc_empty[2]
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+  __shared__ int n_row_tiles;
+  __shared__ int rt_expert[GR_MAX_ROW_TILES], rt_row0[GR_MAX_ROW_TILES], rt_rows[GR_MAX_ROW_TILES];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int P = gridDim.x, cta = blockIdx.x;
+  const int nkb = (p.K + TILE_K - 1) / TILE_K;
+  const int tiles_n = (p.N + TILE_N - 1) / TILE_N;
+
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto acc_full_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
+  auto acc_empty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 2 + b); };
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    prefetch_tensormap(&tmap_w);
+    prefetch_tensormap(&tmap_x);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full_bar(b), 1);
+      mbar_init(acc_empty_bar(b), 4);  // one arrival per epilogue warp
+    }
+    fence_barrier_init();
+    int n = 0, first = 0;
+    for (int e = 0; e < g.n_exp; ++e) {
+      const int c = g.counts[e];
+      for (int r = 0; r < c && n < GR_MAX_ROW_TILES; r += BT) {
+        rt_expert[n] = e;
+        rt_row0[n] = first + r;
+        rt_rows[n] = min(BT, c - r);
+        ++n;
+      }
+      first += c;
+    }
+    n_row_tiles = n;
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&tmem_slot), Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+  volatile int* abort_p = &abort_flag;
+  const long long wait_limit = p.wait_cycles > 0 ? p.wait_cycles : WAIT_LIMIT_CYCLES;
+  const long long n_tiles = (long long)n_row_tiles * tiles_n;      // row tile major: a wave shares a few row tiles
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int s = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (long long tile = cta; ok && tile < n_tiles; tile += P) {
+        const int rt = (int)(tile / tiles_n), n0 = (int)(tile % tiles_n) * TILE_N;
+        const int w_row = rt_expert[rt] * g.w_rows + n0, x_row = rt_row0[rt];
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!mbar_wait(empty_bar(s), phase ^ 1, abort_p, wait_limit)) {
+            abort_flag = 1;
+            atomicExch(p.err, 10);
+            ok = false;
+            break;
+          }
+          const uint32_t a = smem_base + s * Cfg::STAGE_BYTES;
+          mbar_expect_tx(full_bar(s), Cfg::STAGE_BYTES);
+          tma_load_2d(a, &tmap_w, full_bar(s), kb * TILE_K, w_row);
+          if (DUAL) tma_load_2d(a + A_BYTES, &tmap_w, full_bar(s), kb * TILE_K, w_row + p.dual_offset);
+          tma_load_2d(a + A_BYTES * (DUAL ? 2 : 1), &tmap_x, full_bar(s), kb * TILE_K, x_row);
+          if (++s == STAGES) {
+            s = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_16bit(TILE_N, BT, p.half != 0);
+      int s = 0;
+      uint32_t phase = 0;
+      int seg = 0;
+      bool ok = true;
+      for (long long tile = cta; ok && tile < n_tiles; tile += P, ++seg) {
+        const int buf = seg & 1, use = seg >> 1;
+        if (!mbar_wait(acc_empty_bar(buf), (use & 1) ^ 1, abort_p, wait_limit)) {
+          abort_flag = 1;
+          atomicExch(p.err, 13);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d0 = tmem_base + buf * Cfg::ACC_COLS;
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!mbar_wait(full_bar(s), phase, abort_p, wait_limit)) {
+            abort_flag = 1;
+            atomicExch(p.err, 11);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a = smem_base + s * Cfg::STAGE_BYTES;
+          const uint64_t a_desc = umma_desc_k_sw128(a);
+          const uint64_t a2_desc = umma_desc_k_sw128(a + A_BYTES);
+          const uint64_t b_desc = umma_desc_k_sw128(a + A_BYTES * (DUAL ? 2 : 1));
+#pragma unroll
+          for (int kk = 0; kk < TILE_K / UMMA_K; ++kk) {
+            const bool acc = kb > 0 || kk > 0;
+            const uint64_t adv = (uint64_t)(kk * UMMA_K * 2 >> 4);  // 32 bytes per step, in 16-byte units
+            umma_bf16(d0, a_desc + adv, b_desc + adv, idesc, acc);
+            if (DUAL) umma_bf16(d0 + BT, a2_desc + adv, b_desc + adv, idesc, acc);
+          }
+          umma_commit(empty_bar(s));  // the stage is free once these MMAs have read it
+          if (++s == STAGES) {
+            s = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) umma_commit(acc_full_bar(buf));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int quarter = warp & 3;  // the TMEM lanes this warp may read: 32*quarter .. +31
+    const int n_local = quarter * 32 + lane;
+    const int ep_tid = threadIdx.x - 64;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    TcParams q = p;
+    int seg = 0;
+    for (long long tile = cta; tile < n_tiles; tile += P, ++seg) {
+      const int buf = seg & 1, use = seg >> 1;
+      bool ok = mbar_wait(acc_full_bar(buf), use & 1, abort_p, wait_limit);
+      if (!ok) abort_flag = 1;
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // the four warps agree on going on
+      if (abort_flag) {
+        if (ep_tid == 0) atomicExch(p.err, 12);
+        break;
+      }
+      tc_fence_after();
+      const int rt = (int)(tile / tiles_n), n0 = (int)(tile % tiles_n) * TILE_N;
+      const int t0 = rt_row0[rt], rows = rt_rows[rt];
+      q.M = t0 + rows;                                  // rows past the group are another expert's: not stored
+      const int n = n0 + n_local;
+      const uint32_t acc_addr = lane_addr + buf * Cfg::ACC_COLS;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BT && c0 < rows; c0 += 16) {
+        float v0[16], v1[16];
+        tmem_ld16(acc_addr + c0, v0);
+        if (DUAL) tmem_ld16(acc_addr + BT + c0, v1);
+        if (n < p.N) tc_apply16(q, t0 + c0, n, v0, DUAL ? v1 : v0);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty_bar(buf));
+    }
+    tc_fence_before();
+  }
+
+  __syncthreads();
+  if (abort_flag && threadIdx.x == 0) {
+    // let TMA copies that were already issued land before the CTA's shared memory goes away
+    const long long t0c = clock64();
+    while (clock64() - t0c < 2000000LL) {
+    }
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+template <bool DUAL>
+static int launch_tc_grouped(const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& p, const GroupedParams& g, int n_ctas,
+                             cudaStream_t stream) {
+  using Cfg = TcConfig<GR_BT, DUAL>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_grouped_kernel<DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    FERRUM_CHECK_ARG(e == cudaSuccess, "gemm_tc_grouped: cannot reserve %d bytes of shared memory: %s", Cfg::SMEM_BYTES,
+                     cudaGetErrorString(e));
+    configured = true;
+  }
+  gemm_tc_grouped_kernel<DUAL><<<n_ctas, 192, Cfg::SMEM_BYTES, stream>>>(mw, mx, p, g);
+  FERRUM_CHECK_LAUNCH("gemm_tc_grouped");
+  return 0;
+}
+
+// 1 when ferrum_gemm_tc_grouped takes these operands (16-byte rows and bases, not more row tiles than its table holds).
+FERRUM_API int ferrum_gemm_tc_grouped_supported(const void* x, const void* w, int n_rows, int n_exp, int K, int ldx) {
+  return K % 8 == 0 && ldx % 8 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0 &&
+         (n_rows + GR_BT - 1) / GR_BT + n_exp <= GR_MAX_ROW_TILES;
+}
+
+// x [x_rows, ldx] (the first n_rows sorted by expert), w [n_exp, w_rows, K] dense, counts [n_exp] on the device.
+// glu: 0 float32 rows out [n_rows, ldo]; 1 / 2: silu / gelu_tanh of the gate rows times the up rows (rows N + n), out in the
+// operands' type.
+FERRUM_API int ferrum_gemm_tc_grouped(const void* x, const void* w, void* out, int dtype, int n_rows, int x_rows, int N, int K,
+                                      int ldx, int ldo, int n_exp, int w_rows, const int* counts, int glu, int* err_flag,
+                                      cudaStream_t stream) {
+  FERRUM_CHECK_ARG(n_rows >= 0 && N > 0 && K > 0 && n_exp > 0, "gemm_tc_grouped: bad sizes");
+  FERRUM_CHECK_ARG(ferrum_is_16bit(dtype), "gemm_tc_grouped: dtype code %d is not a 16-bit type", dtype);
+  FERRUM_CHECK_ARG(err_flag != nullptr && counts != nullptr, "gemm_tc_grouped: the error flag and the counters are required");
+  if (n_rows == 0) return 0;
+  FERRUM_CHECK_ARG(ferrum_gemm_tc_grouped_supported(x, w, n_rows, n_exp, K, ldx), "gemm_tc_grouped: rows must be 16-byte multiples "
+                   "on 16-byte boundaries, and at most %d row tiles", GR_MAX_ROW_TILES);
+  FERRUM_CHECK_ARG(ldx >= K && ldo >= N && x_rows >= n_rows && w_rows >= (glu ? 2 * N : N), "gemm_tc_grouped: shapes do not agree");
+  const bool dual = glu != 0;
+  TcParams p{out, nullptr, nullptr, err_flag, n_rows, N, K, ldo, dual ? TC_SWIGLU : TC_STORE_F32, dual ? N : 0, 0};
+  p.half = dtype == FERRUM_F16;
+  p.wait_cycles = g_wait_cycles;
+  p.glu_act = glu == 2 ? 1 : 0;
+  GroupedParams g{counts, n_exp, w_rows};
+  CUtensorMap mw, mx;
+  if (int r = get_tensor_map(w, (long long)n_exp * w_rows, K, K, TILE_N, &mw)) return r;
+  if (int r = get_tensor_map(x, x_rows, K, ldx, GR_BT, &mx)) return r;
+  const long long tiles_bound = (long long)((n_rows + GR_BT - 1) / GR_BT + n_exp) * ((N + TILE_N - 1) / TILE_N);
+  int n_ctas = sm_count();
+  if (n_ctas > tiles_bound) n_ctas = (int)tiles_bound;
+  return dual ? launch_tc_grouped<true>(mw, mx, p, g, n_ctas, stream) : launch_tc_grouped<false>(mw, mx, p, g, n_ctas, stream);
+}
+
 FERRUM_TRACE_READER(ferrum_trace_gemm)

@@ -26,7 +26,7 @@ TC_STORE_BF16, TC_STORE_F32, TC_RESIDUAL, TC_SWIGLU, TC_GEGLU = 0, 1, 2, 3, 4   
 
 _lib = None
 _lock = threading.Lock()
-ABI = 15
+ABI = 16
 
 
 def lib():
@@ -984,10 +984,21 @@ def moe_route(logits, n_tokens, n_exp, top, x, scale_input, expert_of, rank_of, 
     launches += 1          # (the entry point launches the routing and the gather)
 
 
-def moe_gemm(a, w, counts, n_rows, out, N, glu=None):
+_moe_tcgen05 = True
+
+
+def set_moe_tcgen05(on: bool):
+    """Tests and measurements: False keeps the grouped products of many rows on the mma.sync kernel."""
+    global _moe_tcgen05
+    _moe_tcgen05 = bool(on)
+
+
+def moe_gemm(a, w, counts, n_rows, out, N, glu=None, err=None):
     """out[row] = a[row] @ w[expert of row].T over rows sorted by expert (`counts` rows each, on the device).
     w: [n_exp, rows, K]; glu ("silu" / "gelu_tanh"): w holds N gate rows then N up rows per expert and out
-    (compute type) gets act(gate) * up; else out is float32 [n_rows, N]."""
+    (compute type) gets act(gate) * up; else out is float32 [n_rows, N].  With `err` (the step's error flag) 16-bit
+    products of many rows (more than about 32 an expert) run on the tcgen05 kernel, the others on mma.sync tiles
+    or, float32 and unaligned rows, on the CUDA cores."""
     _need(a, None, "a", 2); _need(w, a.dtype, "w", 3); _need(out, a.dtype if glu else torch.float32, "out", 2)
     n_exp, w_rows, K = w.shape
     if not w.is_contiguous() or a.shape[1] != K or a.shape[0] < n_rows or out.shape[0] < n_rows or out.shape[1] < N:
@@ -996,6 +1007,12 @@ def moe_gemm(a, w, counts, n_rows, out, N, glu=None):
     if _profile is not None:
         _work = (w.numel() * w.element_size() + n_rows * (K * a.element_size() + N * out.element_size()),
                  2.0 * n_rows * K * N * (2 if glu else 1))
+    if (err is not None and _moe_tcgen05 and a.dtype in SIXTEEN_BIT and n_rows > 32 * n_exp and w_rows == (2 * N if glu else N)
+            and lib().ferrum_gemm_tc_grouped_supported(_ptr(a), _ptr(w), c_int(n_rows), c_int(n_exp), c_int(K), c_int(a.stride(0)))):
+        _check(lib().ferrum_gemm_tc_grouped(_ptr(a), _ptr(w), _ptr(out), dtype_code(a.dtype), c_int(n_rows), c_int(a.shape[0]), c_int(N),
+                                            c_int(K), c_int(a.stride(0)), c_int(out.stride(0)), c_int(n_exp), c_int(w_rows), _ptr(counts),
+                                            c_int(1 + GLU_ACTS[glu] if glu else 0), _ptr(err), _stream()), "moe_gemm")
+        return
     _check(lib().ferrum_moe_gemm(_ptr(a), c_int(a.stride(0)), _ptr(w), c_int(w_rows), c_int(K), c_int(N), c_int(n_exp), _ptr(counts),
                                  c_int(n_rows), dtype_code(a.dtype), c_int(1 if glu else 0), c_int(GLU_ACTS[glu] if glu else 0),
                                  _ptr(out), c_int(out.stride(0)), _stream()), "moe_gemm")

@@ -162,9 +162,9 @@ class RoutedFeedForward(FeedForward):
         ops.moe_route(logits, T, n, top, x, self.scale_input, expert_of, rank_of, weight_of, counts, xg, row_of,
                       scores=self.scores, renormalize=self.renormalize)
         act = ctx.buf("moe_act", (cap * top, self.hidden), self.dtype)
-        ops.moe_gemm(xg, self.w_gate_up, counts, T * top, act, self.hidden, glu=self.act)
+        ops.moe_gemm(xg, self.w_gate_up, counts, T * top, act, self.hidden, glu=self.act, err=ctx.err)
         rows = ctx.buf("moe_rows", (cap * top, self.width), torch.float32)
-        ops.moe_gemm(act, self.w_down, counts, T * top, rows, self.width)
+        ops.moe_gemm(act, self.w_down, counts, T * top, rows, self.width, err=ctx.err)
         self._weight_of = weight_of
         return rows, row_of, top
 

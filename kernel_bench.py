@@ -11,7 +11,7 @@ peaks.  This is the small case that `ncu` captures are taken on.
     python kernel_bench.py head_linear --tokens 8 --hq 16 --n 512 --k 128
     python kernel_bench.py attn_decode|attn_prefill --exact [--window W] [--penalty]   (float32 weights and sums on 16-bit storage)
     python kernel_bench.py ssm --tokens 2048 [--batch 1] [--hq 64] [--head-dim 64] [--state 128]   (the state-space mixer's kernels)
-    python kernel_bench.py moe --tokens 4096 --n 2816 --k 2048 [--experts 8] [--epilogue store|swiglu] [--cuda-cores]   (grouped product of a routed feed-forward)
+    python kernel_bench.py moe --tokens 4096 --n 2816 --k 2048 [--experts 8] [--epilogue store|swiglu] [--mma-sync] [--cuda-cores]   (grouped product of a routed feed-forward)
     python kernel_bench.py streams --tokens 2048 --k 2048 [--streams 4]   (write, read and norm over the residual streams)
     python kernel_bench.py rmsnorm|rope --tokens 8
     python kernel_bench.py step --tokens 2048 [--layers 2] [--dtype bf16|fp16|fp32]   (one prompt portion through the model)
@@ -47,6 +47,7 @@ def main():
     ap.add_argument("--exact", action="store_true", help="attn_*: the CUDA-core kernel with float32 results, as the shaped attention runs it")
     ap.add_argument("--penalty", action="store_true", help="attn_* --exact: with a distance penalty per head")
     ap.add_argument("--streams", type=int, default=4, help="streams: copies of the residual stream")
+    ap.add_argument("--mma-sync", action="store_true", help="moe: many rows on the mma.sync kernel instead of the tcgen05 one")
     ap.add_argument("--experts", type=int, default=8, help="moe: experts that share the rows")
     ap.add_argument("--state", type=int, default=128, help="ssm: state elements per head and value element")
     ap.add_argument("--batch", type=int, default=8)
@@ -225,7 +226,9 @@ def main():
         weights = [torch.randn(X, N * (2 if glu else 1), K, device=dev, generator=gen).mul_(0.02).to(td) for _ in range(args.copies)]
         o = torch.empty(R, N, device=dev, dtype=td if glu else torch.float32)
         ops.set_moe_cuda_cores(args.cuda_cores)
-        runs = [lambda w=w: ops.moe_gemm(a, w, counts, R, o, N, glu="silu" if glu else None) for w in weights]
+        ops.set_moe_tcgen05(not args.mma_sync)
+        err = torch.zeros(1, dtype=torch.int32, device=dev)
+        runs = [lambda w=w: ops.moe_gemm(a, w, counts, R, o, N, glu="silu" if glu else None, err=err) for w in weights]
         work = {"bytes": weights[0].numel() * esize + R * K * esize + o.numel() * o.element_size(),
                 "flops": 2.0 * R * N * K * (2 if glu else 1), "bound": "hbm" if R <= 32 * X else "tensor"}
     elif args.kernel == "streams":

@@ -359,13 +359,14 @@ def test_one_stream_with_ones_is_the_plain_residual_sum(cuda):
 # ================================================================= the routed feed-forward alone
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("E,F,n_exp,top,T", [(52, 20, 5, 2, 37), (128, 64, 4, 1, 300), (40, 24, 1, 1, 9), (64, 32, 16, 4, 70), (72, 100, 40, 8, 11),
-                                             (320, 96, 8, 1, 2), (200, 88, 3, 2, 700), (264, 168, 6, 1, 150)])
+                                             (320, 96, 8, 1, 2), (200, 88, 3, 2, 700), (264, 168, 6, 1, 150), (256, 136, 2, 2, 500)])
 def test_routed_feed_forward_alone(cuda, dtype, E, F, n_exp, top, T):
     """Router, choice, gather, both grouped products and the sum against the plain function; with more
     experts than tokens some experts get no row, with one expert all rows are its.  In bfloat16 the sizes
-    that are multiples of 8 take the tensor-core product (few rows an expert: tiles of 16 rows; many: of
-    128, several per expert, with ragged last tiles and feature counts that end inside a tile), the others
-    the CUDA-core one."""
+    that are multiples of 8 take a tensor-core product (few rows an expert: mma.sync tiles of 16 rows; many:
+    the tcgen05 kernel with tiles of 128 rows, several per expert, with ragged last tiles, feature counts
+    and a K that end inside a tile), the others a CUDA-core one.  The 16-bit kernels are compared with
+    each other too."""
     from ferrum_b200.parts import RoutedFeedForward
     td = TD[dtype]
     ff = RoutedFeedForward(E, F, n_exp, top, td)
@@ -390,13 +391,20 @@ def test_routed_feed_forward_alone(cuda, dtype, E, F, n_exp, top, T):
         # both kernels of the grouped product see the same 16-bit operands and sum in float32: they agree far closer
         # than either does with the plain function (an activation may round the other way now and then)
         from ferrum_b200.ops import lib as ops
-        y2 = torch.zeros(T, E, device="cuda")
+        y2, y3 = torch.zeros(T, E, device="cuda"), torch.zeros(T, E, device="cuda")
         ops.set_moe_cuda_cores(True)
         try:
             ff.forward(x, ctx, y2, accumulate=False)
         finally:
             ops.set_moe_cuda_cores(False)
+        ops.set_moe_tcgen05(False)
+        try:
+            ff.forward(x, ctx, y3, accumulate=False)
+        finally:
+            ops.set_moe_tcgen05(True)
+        assert ctx.err.item() == 0
         assert (y2 - y[:T]).abs().max() < 4e-3 * ref.abs().max()
+        assert (y3 - y[:T]).abs().max() < 4e-3 * ref.abs().max()
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -60,6 +60,38 @@ def test_a_wait_that_runs_out_becomes_an_error_code(ops, M, N, K, dual):
     assert ((out.double() - ref).abs() <= torch.clamp(1e-2 * ref.abs().clamp(min=1.0), min=1e-6)).all()
 
 
+@pytest.mark.parametrize("glu", [None, "silu"])
+def test_a_wait_of_the_grouped_product_that_runs_out_becomes_an_error_code(ops, glu):
+    """The same for the grouped tensor-core product (rows sorted by expert): its producer requests nothing, the
+    waits are cut short, the kernel raises an error code between 10 and 13 and returns; the same launch with the
+    hooks off is then correct, on the same context."""
+    g = torch.Generator(device="cuda").manual_seed(52)
+    n_exp, N, K = 3, 136, 200
+    counts = torch.tensor([150, 0, 170], dtype=torch.int32, device="cuda")
+    rows = 320
+    a = torch.randn(rows + 5, K, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(n_exp, (2 if glu else 1) * N, K, device="cuda", generator=g) * 0.1).bfloat16()
+    out = torch.zeros(rows, N, device="cuda", dtype=torch.bfloat16 if glu else torch.float32)
+    e = torch.zeros(1, dtype=torch.int32, device="cuda")
+
+    def launch():
+        ops.moe_gemm(a, w, counts, rows, out, N, glu=glu, err=e)
+        torch.cuda.synchronize()
+
+    ops.gemm_tc_test_hooks(wait_cycles=200_000, drop_loads=True)
+    launch()
+    assert 10 <= e.item() <= 13, e.item()
+    ops.gemm_tc_test_hooks()
+    e.zero_()
+    launch()
+    assert e.item() == 0
+    expert = torch.tensor([0] * 150 + [2] * 170, device="cuda")
+    ref = torch.einsum("rk,rnk->rn", a[:rows].double(), w.double()[expert])
+    if glu:
+        ref = ref[:, :N] / (1 + torch.exp(-ref[:, :N])) * ref[:, N:]
+    assert ((out.double() - ref).abs() <= torch.clamp(1e-2 * ref.abs().clamp(min=1.0), min=1e-6)).all()
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("what", ["write", "read"])
 def test_a_missing_page_fails_the_step_and_nothing_else(cuda, model_dirs, dtype, what, monkeypatch):

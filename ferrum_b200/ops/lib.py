@@ -985,6 +985,7 @@ def moe_route(logits, n_tokens, n_exp, top, x, scale_input, expert_of, rank_of, 
 
 
 _moe_tcgen05 = True
+MOE_TCGEN05_ROWS_PER_EXPERT = 32      # more rows an expert than this on average: the tcgen05 grouped product
 
 
 def set_moe_tcgen05(on: bool):
@@ -1007,7 +1008,7 @@ def moe_gemm(a, w, counts, n_rows, out, N, glu=None, err=None):
     if _profile is not None:
         _work = (w.numel() * w.element_size() + n_rows * (K * a.element_size() + N * out.element_size()),
                  2.0 * n_rows * K * N * (2 if glu else 1))
-    if (err is not None and _moe_tcgen05 and a.dtype in SIXTEEN_BIT and n_rows > 32 * n_exp and w_rows == (2 * N if glu else N)
+    if (err is not None and _moe_tcgen05 and a.dtype in SIXTEEN_BIT and n_rows > MOE_TCGEN05_ROWS_PER_EXPERT * n_exp and w_rows == (2 * N if glu else N)
             and lib().ferrum_gemm_tc_grouped_supported(_ptr(a), _ptr(w), c_int(n_rows), c_int(n_exp), c_int(K), c_int(a.stride(0)))):
         _check(lib().ferrum_gemm_tc_grouped(_ptr(a), _ptr(w), _ptr(out), dtype_code(a.dtype), c_int(n_rows), c_int(a.shape[0]), c_int(N),
                                             c_int(K), c_int(a.stride(0)), c_int(out.stride(0)), c_int(n_exp), c_int(w_rows), _ptr(counts),

@@ -566,8 +566,8 @@ def stream_configs(size, layers, vocab=32000, window=1024):
     s = STREAM_SIZES[size]
     att = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["vdim"], "scale": s["dim"] ** -0.5,
            "mask": {"size": window}, "v_mix": True}
-    windowed = {"type": "attention", "mixer": dict(att, q_temp={"coef": 0.5, "every": 128})}
-    chunked = {"type": "attention_2", "mixer": dict(att, rot={"base": 10000.0, "dims": s["dim"] // 2, "scaling": {"factor": 8.0}})}
+    windowed = {"type": "attention", "mixer": dict(att, q_temp={"coef": 0.25, "every": 256})}
+    chunked = {"type": "attention_2", "mixer": dict(att, rot={"base": 10000.0, "dims": s["dim"] // 2, "scaling": {"factor": 4.0}})}
     dense = {"kind": "dense", "ff": s["ff"]}
     routed = {"kind": "moe", "expert": {"ff": s["expert_ff"]}, "router": {"experts": s["experts"], "top": s["top"]}}
     kinds = [dict(windowed, mlp=dense), dict(chunked, mlp=routed), dict(windowed, mlp=routed), dict(chunked, mlp=dense)]

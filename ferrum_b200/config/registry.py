@@ -91,3 +91,5 @@ def _ensure_builtin():
         from ..models import vikupel  # noqa: F401
     if "Zavesun" not in _REGISTRY:
         from ..models import zavesun  # noqa: F401
+    if "Pererax" not in _REGISTRY:
+        from ..models import pererax  # noqa: F401

@@ -23,7 +23,10 @@
 // weighted sum of V (crates/model/src/llama.rs:220-247; crates/kernels/src/scalar.rs:125-141).
 // `window` > 0 keeps keys in (pos-window, pos]; with `chunked` the same number is the length of a
 // chunk instead: positions are cut into chunks of `window` from position 0 and a query sees the
-// keys of its own chunk up to itself.
+// keys of its own chunk up to itself.  `softcap` c > 0 bends the scaled score to c * tanh(score / c)
+// (before any distance penalty).  `sink`: a key of score 0 without a value joins every row's softmax,
+// weight_j = exp(s_j) / (exp(0) + sum exp(s)); it enters once, where a row's (maximum, sum, values)
+// are final: in the walking kernels' last step, or in the fold of the splits.
 #include "common.cuh"
 
 constexpr int AG_WARPS = 4;
@@ -98,6 +101,20 @@ __device__ __forceinline__ float ag_distance_penalty(const float* bias1, const f
   return bias2 == nullptr ? bias1[h] * (float)dist : bias1[h] * log1pf(bias2[h] * (float)dist);
 }
 
+// The scaled score, bent by the soft cap when there is one.
+__device__ __forceinline__ float ag_score(float dot, float scale, float softcap) {
+  const float s = dot * scale;
+  return softcap > 0.f ? softcap * tanhf(s / softcap) : s;
+}
+
+// The divisor of a finished row (maximum m, sum l of exp(s - m)) with the sink's exp(0 - m) added; `f` receives
+// the factor for the weighted values (they were summed relative to m).  Relative to max(m, 0) nothing overflows.
+__device__ __forceinline__ float ag_sink_sum(float m, float l, float* f) {
+  const float top = fmaxf(m, 0.f);
+  *f = m == -INFINITY ? 0.f : expf(m - top);
+  return l * *f + expf(-top);
+}
+
 // The first key a query at `pos` sees: a sliding window of `window` keys, or (chunked) the start of its chunk.
 __device__ __forceinline__ int ag_first_key(int pos, int window, int chunked) {
   if (window <= 0) return 0;
@@ -116,7 +133,8 @@ attention_generic_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, 
                          const int* __restrict__ block_table, int table_width, const T* __restrict__ kv_plane,
                          long long page_stride, int page_size, int Hq, int Hkv, int D, float scale, int window,
                          int* __restrict__ err, float* __restrict__ part, int split_slots, int vec,
-                         const float* __restrict__ bias1, const float* __restrict__ bias2, int out_f32, int chunked) {
+                         const float* __restrict__ bias1, const float* __restrict__ bias2, int out_f32, int chunked,
+                         float softcap, int sink) {
   using Tile = AgTile<DI>;
   constexpr int TK = Tile::TK, DP = Tile::DP, KS = Tile::KS;
   extern __shared__ __align__(16) float ag_smem[];
@@ -273,7 +291,7 @@ attention_generic_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, 
           dot = fmaf(a.z, k4.z, dot);
           dot = fmaf(a.w, k4.w, dot);
         }
-        s = dot * scale - ag_distance_penalty(bias1, bias2, h0 + warp, pos - (k_begin + n * TK + lane));
+        s = ag_score(dot, scale, softcap) - ag_distance_penalty(bias1, bias2, h0 + warp, pos - (k_begin + n * TK + lane));
       }
       const float m_new = fmaxf(m, warp_max(s));
       float corr = 1.f, pj = 0.f;
@@ -312,10 +330,12 @@ attention_generic_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, 
   if (warp >= nh) return;
   const int h = h0 + warp;
   if (part == nullptr) {
+    float f = 1.f;
+    if (sink) l = ag_sink_sum(m, l, &f);
 #pragma unroll
     for (int i = 0; i < DI; ++i) {
       const int d = lane + 32 * i;
-      if (d < D) ag_store<T>(out, (size_t)t * ldo + (size_t)h * D + d, l > 0.f ? acc[i] / l : 0.f, out_f32);
+      if (d < D) ag_store<T>(out, (size_t)t * ldo + (size_t)h * D + d, l > 0.f ? acc[i] * f / l : 0.f, out_f32);
     }
   } else {
     float* p = part + (((size_t)t * Hq + h) * split_slots + blockIdx.y) * (D + 2);
@@ -365,7 +385,7 @@ attention_generic_tokens_kernel(const T* __restrict__ q, int ldq, T* __restrict_
                                 const int* __restrict__ block_table, int table_width, const T* __restrict__ kv_plane,
                                 long long page_stride, int page_size, int Hq, int Hkv, int D, float scale, int window,
                                 int* __restrict__ err, int vec, const float* __restrict__ bias1,
-                                const float* __restrict__ bias2, int out_f32, int chunked) {
+                                const float* __restrict__ bias2, int out_f32, int chunked, float softcap, int sink) {
   using Tile = AgTile<DI>;
   using TT = AgTokenTile<DI>;
   constexpr int TK = Tile::TK, DP = Tile::DP, KS = Tile::KS;
@@ -522,7 +542,7 @@ attention_generic_tokens_kernel(const T* __restrict__ q, int ldq, T* __restrict_
 #pragma unroll
       for (int i = 0; i < AG_TH; ++i) {
         const bool seen = have && key <= pos[i] && key >= lo[i];
-        const float sv = seen ? sc[i] * scale - ag_distance_penalty(bias1, bias2, h0 + warp, pos[i] - key) : -INFINITY;
+        const float sv = seen ? ag_score(sc[i], scale, softcap) - ag_distance_penalty(bias1, bias2, h0 + warp, pos[i] - key) : -INFINITY;
         const float m_new = fmaxf(m[i], warp_max(sv));
         float cr = 1.f, pj = 0.f;
         if (m_new != -INFINITY) {
@@ -569,10 +589,12 @@ attention_generic_tokens_kernel(const T* __restrict__ q, int ldq, T* __restrict_
 #pragma unroll
   for (int i = 0; i < AG_TH; ++i) {
     if (i0 + i >= nt) break;
+    float f = 1.f, li = l[i];
+    if (sink) li = ag_sink_sum(m[i], li, &f);
 #pragma unroll
     for (int e = 0; e < DI; ++e) {
       const int d = lane + 32 * e;
-      if (d < D) ag_store<T>(out, (size_t)(t0 + i0 + i) * ldo + (size_t)h * D + d, l[i] > 0.f ? acc[i][e] / l[i] : 0.f, out_f32);
+      if (d < D) ag_store<T>(out, (size_t)(t0 + i0 + i) * ldo + (size_t)h * D + d, li > 0.f ? acc[i][e] * f / li : 0.f, out_f32);
     }
   }
 }
@@ -581,7 +603,7 @@ attention_generic_tokens_kernel(const T* __restrict__ q, int ldq, T* __restrict_
 template <typename T>
 __global__ void __launch_bounds__(32)
 attention_generic_combine_kernel(T* __restrict__ out, int ldo, const float* __restrict__ part, const int* __restrict__ positions,
-                                 int Hq, int D, int window, int split_slots, int out_f32, int chunked) {
+                                 int Hq, int D, int window, int split_slots, int out_f32, int chunked, int sink) {
   const int t = blockIdx.x, h = blockIdx.y, lane = threadIdx.x;
   const int pos = positions[t];
   const int lo = ag_first_key(pos, window, chunked);
@@ -617,10 +639,12 @@ attention_generic_combine_kernel(T* __restrict__ out, int ldo, const float* __re
       M = m_new;
     }
   }
+  float f = 1.f;
+  if (sink) L = ag_sink_sum(M, L, &f);
 #pragma unroll
   for (int i = 0; i < AG_DI; ++i) {
     const int d = lane + 32 * i;
-    if (d < D) ag_store<T>(out, (size_t)t * ldo + (size_t)h * D + d, L > 0.f ? O[i] / L : 0.f, out_f32);
+    if (d < D) ag_store<T>(out, (size_t)t * ldo + (size_t)h * D + d, L > 0.f ? O[i] * f / L : 0.f, out_f32);
   }
 }
 
@@ -634,6 +658,7 @@ FERRUM_API int ferrum_attention_generic_split() { return AG_SPLIT; }
 // and a second launch folds the partials into `out`.
 // bias1, bias2 (float32 per query head on the device, or null): the distance penalty above.  out_f32: the
 // output rows are float32 whatever the cache's type.  chunked: `window` is a chunk length (see the top).
+// softcap, sink: see the top.
 // q_start (n_reqs + 1 entries on the device; may be null): with it and without `part`, tokens of a
 // request that follow each other in the batch share their key tiles (the kernel for prompt portions).
 FERRUM_API int ferrum_attention_generic(const void* q, int ldq, void* out, int ldo, int dtype, int n_tokens,
@@ -641,7 +666,8 @@ FERRUM_API int ferrum_attention_generic(const void* q, int ldq, void* out, int l
                                         int table_width, const void* kv_plane, long long page_stride, int page_size,
                                         int Hq, int Hkv, int D, float scale, int window, int* err_flag, float* part,
                                         int split_slots, const int* q_start, int n_reqs, const float* bias1,
-                                        const float* bias2, int out_f32, int chunked, cudaStream_t stream) {
+                                        const float* bias2, int out_f32, int chunked, float softcap, int sink,
+                                        cudaStream_t stream) {
   FERRUM_CHECK_ARG(n_tokens >= 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0, "attention: bad head counts Hq=%d Hkv=%d", Hq, Hkv);
   FERRUM_CHECK_ARG(D > 0 && D <= AG_MAX_D, "attention: head size %d is outside (0, %d]", D, AG_MAX_D);
   FERRUM_CHECK_ARG(page_size > 0 && table_width > 0 && window >= 0, "attention: bad cache arguments");
@@ -670,7 +696,7 @@ FERRUM_API int ferrum_attention_generic(const void* q, int ldq, void* out, int l
     }                                                                                                                   \
     attention_generic_tokens_kernel<T, DI_><<<(unsigned)ctas, AG_TWARPS * 32, AgTokenTile<DI_>::SMEM_BYTES, stream>>>(   \
       (const T*)q, ldq, (T*)out, ldo, positions, q_start, n_reqs, block_table, table_width, (const T*)kv_plane,         \
-      page_stride, page_size, Hq, Hkv, D, scale, window, err_flag, vec, bias1, bias2, out_f32, chunked);                                          \
+      page_stride, page_size, Hq, Hkv, D, scale, window, err_flag, vec, bias1, bias2, out_f32, chunked, softcap, sink);                                        \
   })
     if (D <= 32) AG_LAUNCH_TOKENS(1);
     else if (D <= 64) AG_LAUNCH_TOKENS(2);
@@ -693,7 +719,7 @@ FERRUM_API int ferrum_attention_generic(const void* q, int ldq, void* out, int l
     }                                                                                                                   \
     attention_generic_kernel<T, DI_><<<grid, AG_WARPS * 32, AgTile<DI_>::SMEM_BYTES, stream>>>(                        \
       (const T*)q, ldq, (T*)out, ldo, positions, req_of_token, block_table, table_width, (const T*)kv_plane, page_stride, \
-      page_size, Hq, Hkv, D, scale, window, err_flag, part, split_slots, vec, bias1, bias2, out_f32, chunked);                                    \
+      page_size, Hq, Hkv, D, scale, window, err_flag, part, split_slots, vec, bias1, bias2, out_f32, chunked, softcap, sink);                                  \
   })
   if (D <= 32) AG_LAUNCH(1);
   else if (D <= 64) AG_LAUNCH(2);
@@ -705,7 +731,7 @@ FERRUM_API int ferrum_attention_generic(const void* q, int ldq, void* out, int l
     const dim3 cgrid(n_tokens, Hq);
     FERRUM_CHECK_ARG(cgrid.y <= 65535, "attention: too many heads");
     FERRUM_DISPATCH_DTYPE(dtype, T, (attention_generic_combine_kernel<T><<<cgrid, 32, 0, stream>>>(
-        (T*)out, ldo, part, positions, Hq, D, window, split_slots, out_f32, chunked)));
+        (T*)out, ldo, part, positions, Hq, D, window, split_slots, out_f32, chunked, sink)));
     FERRUM_CHECK_LAUNCH("attention_generic_combine");
   }
   return 0;

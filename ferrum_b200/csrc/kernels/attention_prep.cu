@@ -2,7 +2,9 @@
 //
 // qkv_shape: reads one float32 row per token [q heads | k heads | v heads | ...] as a product left
 // it, and per head, in float32, in this order: adds the projection's bias; divides a query or key head
-// by its root mean square and multiplies by a weight vector shared by all heads (`qnorm_w`, `knorm_w`);
+// by its root mean square and multiplies by a weight vector shared by all heads (`qnorm_w`, `knorm_w`), or
+// (`whole_norm`) divides it by the root mean square of the token's WHOLE query (key) projection, all heads at
+// once, and multiplies by a weight vector as long as that projection;
 // turns the leading `rope_dim` elements of a query or key head by the token's position (table of
 // cos/sin per position and pair; pairs (i, i + rope_dim/2) or (2i, 2i+1)); then, when asked, divides
 // the whole head by its root mean square (no weight); multiplies a query head by a temperature of its
@@ -11,7 +13,8 @@
 // (1 - lambda) v + lambda v_first (`vmix_mode` 2), or leaves its own there for later layers (1).
 // Queries go out in the compute type [T, Hq, Dp], keys and values go to the token's place in the
 // paged cache (rows of Dp elements, zero past the head's own size: Dp = max(key size, value size)
-// lets one page layout hold both).
+// lets one page layout hold both).  With `v_from_k` the row has no value heads: the value of a KV head is
+// its key head as the product left it (before bias-free norm and turn), of the key's size.
 //
 // attention_finish: reads the attention's float32 output [T, Hq, Dp]; turns each head back by the
 // query's position (the inverse of the value rotation), multiplies by a sigmoid gate whose logits lie
@@ -34,6 +37,8 @@ struct HeadExtras {
   float* v_first;           // [T, ld_first] float32
   int ld_first;
   const float* v_lambda;    // one float on the device
+  int whole_norm;           // 1: qnorm_w is [Hq*Dk], knorm_w [Hkv*Dk], and the mean square runs over the whole projection
+  int v_from_k;             // 1: the row is [q heads | k heads]; value head g is key head g as projected
 };
 
 template <typename T>
@@ -54,7 +59,8 @@ qkv_shape_kernel(const float* __restrict__ proj, int ldp, int n_tokens, const in
   float* const row = rows[warp];
   const bool is_v = slot >= Hq + Hkv;
   const int D = is_v ? Dv : Dk;
-  const int src_off = slot < Hq ? slot * Dk : (slot < Hq + Hkv ? Hq * Dk + (slot - Hq) * Dk : (Hq + Hkv) * Dk + (slot - Hq - Hkv) * Dv);
+  const int src_off = slot < Hq ? slot * Dk : (slot < Hq + Hkv ? Hq * Dk + (slot - Hq) * Dk :
+                      (x.v_from_k ? Hq * Dk + (slot - Hq - Hkv) * Dk : (Hq + Hkv) * Dk + (slot - Hq - Hkv) * Dv));
   const float* src = proj + (size_t)t * ldp + src_off;
   if (x.bias != nullptr) {
     for (int d = lane; d < D; d += 32) row[d] = src[d] + x.bias[src_off + d];
@@ -63,7 +69,19 @@ qkv_shape_kernel(const float* __restrict__ proj, int ldp, int n_tokens, const in
   }
   __syncwarp();
   const float* nw = is_v ? nullptr : (slot < Hq ? x.qnorm_w : x.knorm_w);
-  if (nw != nullptr) {                       // weighted RMS norm of the head, before any turn
+  if (nw != nullptr && x.whole_norm) {       // RMS norm over all heads of the projection at once, before any turn
+    const int first = slot < Hq ? 0 : Hq * Dk, n = (slot < Hq ? Hq : Hkv) * Dk, head = slot < Hq ? slot : slot - Hq;
+    const float* all = proj + (size_t)t * ldp + first;
+    float ss = 0.f;
+    for (int d = lane; d < n; d += 32) {
+      const float v = all[d] + (x.bias != nullptr ? x.bias[first + d] : 0.f);
+      ss = fmaf(v, v, ss);
+    }
+    ss = warp_sum(ss);
+    const float r = 1.f / sqrtf(ss / (float)n + eps);
+    for (int d = lane; d < D; d += 32) row[d] = row[d] * r * nw[head * Dk + d];
+    __syncwarp();
+  } else if (nw != nullptr) {                // weighted RMS norm of the head, before any turn
     float ss = 0.f;
     for (int d = lane; d < D; d += 32) ss = fmaf(row[d], row[d], ss);
     ss = warp_sum(ss);
@@ -170,7 +188,8 @@ FERRUM_API int ferrum_qkv_shape(const float* proj, int ldp, int n_tokens, const 
                                 void* q_out, int ldq, void* plane, long long page_stride, int page_size, int dtype, int Hq,
                                 int Hkv, int Dk, int Dv, int Dp, int writes, int* err, const float* bias,
                                 const float* qnorm_w, const float* knorm_w, float qtemp_coef, int qtemp_every,
-                                int vmix_mode, float* v_first, int ld_first, const float* v_lambda, cudaStream_t stream) {
+                                int vmix_mode, float* v_first, int ld_first, const float* v_lambda, int whole_norm, int v_from_k,
+                                cudaStream_t stream) {
   FERRUM_CHECK_ARG(Hq > 0 && Hkv > 0 && Dk > 0 && Dv > 0 && Dp >= Dk && Dp >= Dv && Dp <= AP_MAX_D,
                    "qkv_shape: bad head sizes Dk=%d Dv=%d Dp=%d", Dk, Dv, Dp);
   FERRUM_CHECK_ARG(rope_dim >= 0 && rope_dim <= Dk && rope_dim % 2 == 0, "qkv_shape: bad rotary size %d", rope_dim);
@@ -180,7 +199,9 @@ FERRUM_API int ferrum_qkv_shape(const float* proj, int ldp, int n_tokens, const 
   FERRUM_CHECK_ARG(vmix_mode == 0 || (v_first != nullptr && ld_first >= Hkv * Dv && (vmix_mode == 1 || v_lambda != nullptr)),
                    "qkv_shape: value mixing needs the first layer's values and a blend factor");
   if (n_tokens == 0) return 0;
-  const HeadExtras extras{bias, qnorm_w, knorm_w, qtemp_coef, qtemp_every, vmix_mode, v_first, ld_first, v_lambda};
+  FERRUM_CHECK_ARG(!v_from_k || (Dv == Dk && bias == nullptr && cs_v == nullptr && vmix_mode == 0),
+                   "qkv_shape: values taken from the keys have the keys' size, no bias, no turn and no blend");
+  const HeadExtras extras{bias, qnorm_w, knorm_w, qtemp_coef, qtemp_every, vmix_mode, v_first, ld_first, v_lambda, whole_norm, v_from_k};
   const long long items = (long long)n_tokens * (Hq + (writes ? 2 * Hkv : 0));
   const long long blocks = (items + AP_WARPS - 1) / AP_WARPS;
   FERRUM_CHECK_ARG(blocks < (1LL << 31), "qkv_shape: too many rows");

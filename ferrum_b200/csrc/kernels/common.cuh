@@ -151,6 +151,14 @@ __device__ __forceinline__ uint32_t pack2_bits(float lo, float hi, bool half) {
     else FERRUM_CHECK_ARG(false, "dtype code %d is not a 16-bit type", (int)(dtype)); \
   } while (0)
 
+// A gated unit with clamped inputs (activation code 2 of the gated epilogues; 0 is silu and 1 the tanh form of gelu
+// on the gate, times the up value): g = min(gate, limit), u = clamp(up, -limit, limit), g * sigmoid(1.702 g) * (u + 1).
+constexpr int GLU_SWISH_CLAMP = 2;
+__device__ __forceinline__ float glu_swish_clamp(float gate, float up, float limit) {
+  const float g = fminf(gate, limit), u = fminf(fmaxf(up, -limit), limit);
+  return g / (1.f + expf(-1.702f * g)) * (u + 1.f);
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -168,35 +168,39 @@ FERRUM_API int ferrum_norm_pair_shift(const float* x, const float* w1, const flo
 
 // ---------------------------------------------------------------- biased gated linear unit
 // act[t, f] = f(gu[t, f] + bg[f]) * (gu[t, F + f] + bu[f]); gu float32 rows of stride ld, act in the
-// compute dtype.  kind 0: f = silu; 1: f = gelu with the tanh approximation.  Biases may be null.
+// compute dtype.  kind 0: f = silu; 1: f = gelu with the tanh approximation; 2: the clamped unit of common.cuh
+// made of both values and `limit`.  Biases may be null.
 __device__ __forceinline__ float glu_act(float z, int kind) {
   if (kind == 0) return z / (1.0f + expf(-z));
   const float u = 0.7978845608028654f * (z + 0.044715f * z * z * z);
   return 0.5f * z * (1.0f + tanhf(u));
 }
+__device__ __forceinline__ float glu_of(float g, float u, int kind, float limit) {
+  return kind == GLU_SWISH_CLAMP ? glu_swish_clamp(g, u, limit) : glu_act(g, kind) * u;
+}
 
 template <typename TOut>
 __global__ void __launch_bounds__(256)
 bias_glu_kernel(const float* __restrict__ gu, int ld, const float* __restrict__ bg, const float* __restrict__ bu, TOut* __restrict__ act,
-                int ld_out, int F, int kind) {
+                int ld_out, int F, int kind, float limit) {
   pdl_launch();
   pdl_wait();
   const int t = blockIdx.y;
   const float* row = gu + (size_t)t * ld;
   for (int f = blockIdx.x * blockDim.x + threadIdx.x; f < F; f += gridDim.x * blockDim.x) {
     const float g = row[f] + (bg ? bg[f] : 0.f), u = row[F + f] + (bu ? bu[f] : 0.f);
-    act[(size_t)t * ld_out + f] = from_f32<TOut>(glu_act(g, kind) * u);
+    act[(size_t)t * ld_out + f] = from_f32<TOut>(glu_of(g, u, kind, limit));
   }
 }
 
 FERRUM_API int ferrum_bias_glu(const float* gu, int ld, const float* bias_gate, const float* bias_up, void* act, int act_dtype,
-                               int ld_out, int n_tokens, int F, int kind, cudaStream_t stream) {
+                               int ld_out, int n_tokens, int F, int kind, float limit, cudaStream_t stream) {
   FERRUM_CHECK_ARG(n_tokens >= 0 && n_tokens <= 65535 * 32 && F > 0 && ld >= 2 * F && ld_out >= F, "bias glu: bad sizes T=%d F=%d", n_tokens, F);
-  FERRUM_CHECK_ARG(kind == 0 || kind == 1, "bias glu: unknown activation %d", kind);
+  FERRUM_CHECK_ARG(kind >= 0 && kind <= GLU_SWISH_CLAMP, "bias glu: unknown activation %d", kind);
   if (n_tokens == 0) return 0;
   FERRUM_CHECK_ARG(n_tokens <= 65535, "bias glu: too many tokens");
   const dim3 grid(min((F + 255) / 256, 64), n_tokens);
-  FERRUM_DISPATCH_DTYPE(act_dtype, T, launch_kernel(bias_glu_kernel<T>, grid, dim3(256), 0, stream, gu, ld, bias_gate, bias_up, (T*)act, ld_out, F, kind));
+  FERRUM_DISPATCH_DTYPE(act_dtype, T, launch_kernel(bias_glu_kernel<T>, grid, dim3(256), 0, stream, gu, ld, bias_gate, bias_up, (T*)act, ld_out, F, kind, limit));
   FERRUM_CHECK_LAUNCH("bias_glu");
   return 0;
 }
@@ -206,7 +210,7 @@ FERRUM_API int ferrum_bias_glu(const float* gu, int ld, const float* bias_gate, 
 // extra[t, :] (float32) on the way.
 template <typename TOut>
 __global__ void __launch_bounds__(256)
-bias_glu_reduce_kernel(const float* __restrict__ bg, const float* __restrict__ bu, TOut* __restrict__ act, int ld_out, int F, int kind,
+bias_glu_reduce_kernel(const float* __restrict__ bg, const float* __restrict__ bu, TOut* __restrict__ act, int ld_out, int F, int kind, float limit,
                        float* __restrict__ extra, int n_extra, const PartialLayout L) {
   __shared__ PartialTable tab;
   build_partial_table(L, tab);
@@ -216,7 +220,7 @@ bias_glu_reduce_kernel(const float* __restrict__ bg, const float* __restrict__ b
   for (int f = blockIdx.x * blockDim.x + threadIdx.x; f < F + n_extra; f += gridDim.x * blockDim.x) {
     if (f < F) {
       const float g = partial_sum(L, tab, t, f) + (bg ? bg[f] : 0.f), u = partial_sum(L, tab, t, F + f) + (bu ? bu[f] : 0.f);
-      act[(size_t)t * ld_out + f] = from_f32<TOut>(glu_act(g, kind) * u);
+      act[(size_t)t * ld_out + f] = from_f32<TOut>(glu_of(g, u, kind, limit));
     } else {
       extra[(size_t)t * n_extra + (f - F)] = partial_sum(L, tab, t, 2 * F + (f - F));
     }
@@ -224,10 +228,10 @@ bias_glu_reduce_kernel(const float* __restrict__ bg, const float* __restrict__ b
 }
 
 FERRUM_API int ferrum_bias_glu_reduce(const float* bias_gate, const float* bias_up, void* act, int act_dtype, int ld_out, int n_tokens,
-                                      int F, int kind, float* extra, int n_extra, const float* partials, const int* layout,
+                                      int F, int kind, float limit, float* extra, int n_extra, const float* partials, const int* layout,
                                       cudaStream_t stream) {
   FERRUM_CHECK_ARG(n_tokens >= 0 && n_tokens <= 65535 && F > 0 && ld_out >= F && n_extra >= 0, "bias glu: bad sizes T=%d F=%d", n_tokens, F);
-  FERRUM_CHECK_ARG(kind == 0 || kind == 1, "bias glu: unknown activation %d", kind);
+  FERRUM_CHECK_ARG(kind >= 0 && kind <= GLU_SWISH_CLAMP, "bias glu: unknown activation %d", kind);
   FERRUM_CHECK_ARG(n_extra == 0 || extra != nullptr, "bias glu: the extra columns need a place");
   if (n_tokens == 0) return 0;
   PartialLayout L;
@@ -235,7 +239,7 @@ FERRUM_API int ferrum_bias_glu_reduce(const float* bias_gate, const float* bias_
   FERRUM_CHECK_ARG(2 * F + n_extra <= L.tiles * 128 && n_tokens <= L.acc_cols, "bias glu: the partials do not cover the rows");
   const dim3 grid(min((F + n_extra + 255) / 256, 64), n_tokens);
   FERRUM_DISPATCH_DTYPE(act_dtype, T, launch_kernel(bias_glu_reduce_kernel<T>, grid, dim3(256), 0, stream, bias_gate, bias_up, (T*)act, ld_out, F,
-                                                    kind, extra, n_extra, L));
+                                                    kind, limit, extra, n_extra, L));
   FERRUM_CHECK_LAUNCH("bias_glu_reduce");
   return 0;
 }

@@ -42,6 +42,7 @@ enum TcEpilogue : int {
   TC_RESIDUAL = 2,    // out f32  [M, ldo] += acc
   TC_SWIGLU = 3,      // out 16-bit [M, ldo] = silu(acc0) * acc1   (DUAL only)
   TC_GEGLU = 4,       // the same with the tanh form of gelu on acc0 (an entry point's argument; the kernels see TC_SWIGLU and glu_act)
+  TC_SWISH_CLAMP = 5, // the clamped unit (common.cuh) of acc0 and acc1 with the entry point's glu_limit (likewise)
 };
 
 struct TcParams {
@@ -60,13 +61,19 @@ struct TcParams {
   int half;            // 0: operands and 16-bit outputs are bfloat16; 1: float16
   long long wait_cycles;  // limit of every mbarrier wait (0: the default of about a second); tests shorten it
   int drop_loads;      // test hook: the producer requests no tile at all, so that the waits for them run out
-  int glu_act;         // activation of the gate in the SwiGLU epilogues: 0 silu, 1 gelu (tanh form)
+  int glu_act;         // activation of the gate in the SwiGLU epilogues: 0 silu, 1 gelu (tanh form), 2 the clamped unit
+  float glu_limit;     // the clamp of activation 2
 };
 
 // act(gate) of the gated epilogues, float32.
 __device__ __forceinline__ float tc_glu_act(float g, int act) {
   if (act == 1) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
   return g / (1.0f + __expf(-g));
+}
+// What a gated epilogue stores for a gate value and an up value.
+__device__ __forceinline__ float tc_glu(float g, float u, const TcParams& p) {
+  if (p.glu_act == GLU_SWISH_CLAMP) return glu_swish_clamp(g, u, p.glu_limit);
+  return tc_glu_act(g, p.glu_act) * u;
 }
 
 constexpr int TILE_N = 128;  // weight rows per tile (the instruction's M)
@@ -129,7 +136,7 @@ __device__ __forceinline__ void tc_apply16(const TcParams& p, int t_base, int n,
       const bool half = p.half != 0;
 #pragma unroll
       for (int j = 0; j < 16; ++j)
-        if (j < valid) out[j * ld] = bits16(tc_glu_act(a0[j], p.glu_act) * a1[j], half);
+        if (j < valid) out[j * ld] = bits16(tc_glu(a0[j], a1[j], p), half);
       break;
     }
   }
@@ -735,7 +742,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       for (int j = 0; j < 16; ++j) {
         const float theirs = __shfl_xor_sync(0xffffffffu, odd ? v[j] : v[16 + j], 1);
         const float g = odd ? theirs : v[j], up = odd ? v[16 + j] : theirs;
-        st[j * (TILE_N / 2)] = bits16(tc_glu_act(g, p.glu_act) * up, half);
+        st[j * (TILE_N / 2)] = bits16(tc_glu(g, up, p), half);
       }
       stage_send(stage, &tmap_out, false, n0_cta >> 1, t0 + c0);
     };
@@ -946,8 +953,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
             if (p.gated) {  // four neighbouring rows are two (gate, up) pairs
 #pragma unroll
               for (int k = 0; k < 8; ++k) {
-                const uint32_t o2 = pack2_bits(tc_glu_act(acc[k].x, p.glu_act) * acc[k].y,
-                                               tc_glu_act(acc[k].z, p.glu_act) * acc[k].w, p.half != 0);
+                const uint32_t o2 = pack2_bits(tc_glu(acc[k].x, acc[k].y, p), tc_glu(acc[k].z, acc[k].w, p), p.half != 0);
                 *reinterpret_cast<uint32_t*>((uint16_t*)stage + (cg + k) * (TILE_N / 2) + (q4 >> 1)) = o2;
               }
               stage_send(stage, &tmap_out, false, n0 >> 1, t0 + c0);
@@ -1190,7 +1196,7 @@ FERRUM_API long long ferrum_gemm_tc_workspace(int M, int N, int K, int dual, int
 // tile starts at row dual_offset + n.  n_ctas = 0 means one CTA per SM.
 FERRUM_API int ferrum_gemm_tc(const void* x, const void* w, void* out, int dtype, int M, int N, int K, int ldx, int ldw, int ldo,
                               int w_rows, int epilogue, int dual_offset, int n_ctas, float* workspace,
-                              long long workspace_floats, int* counters, int n_counters, int* err_flag,
+                              long long workspace_floats, int* counters, int n_counters, int* err_flag, float glu_limit,
                               cudaStream_t stream) {
   FERRUM_CHECK_ARG(M >= 0 && N > 0 && K > 0, "gemm_tc: bad sizes M=%d N=%d K=%d", M, N, K);
   FERRUM_CHECK_ARG(ferrum_is_16bit(dtype), "gemm_tc: dtype code %d is not a 16-bit type", dtype);
@@ -1201,8 +1207,8 @@ FERRUM_API int ferrum_gemm_tc(const void* x, const void* w, void* out, int dtype
   FERRUM_CHECK_ARG(((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0, "gemm_tc: operands must be 16-byte aligned");
   FERRUM_CHECK_ARG(ldx >= K && ldw >= K && ldo >= N, "gemm_tc: a row stride is shorter than its row");
   const bool dual = dual_offset > 0;
-  const int glu_act = epilogue == TC_GEGLU ? 1 : 0;
-  if (epilogue == TC_GEGLU) epilogue = TC_SWIGLU;
+  const int glu_act = epilogue == TC_GEGLU ? 1 : (epilogue == TC_SWISH_CLAMP ? GLU_SWISH_CLAMP : 0);
+  if (epilogue == TC_GEGLU || epilogue == TC_SWISH_CLAMP) epilogue = TC_SWIGLU;
   FERRUM_CHECK_ARG(dual == (epilogue == TC_SWIGLU), "gemm_tc: the SwiGLU epilogue needs dual_offset, and only it does");
   FERRUM_CHECK_ARG(epilogue >= 0 && epilogue <= 3, "gemm_tc: unknown epilogue %d", epilogue);
   FERRUM_CHECK_ARG(w_rows >= N + dual_offset, "gemm_tc: w has %d rows, needs %d", w_rows, N + dual_offset);
@@ -1223,6 +1229,7 @@ FERRUM_API int ferrum_gemm_tc(const void* x, const void* w, void* out, int dtype
   p.drop_loads = g_drop_loads;
   p.stream_weights = (M + bt - 1) / bt == 1;  // one token tile: no weight tile is read twice
   p.glu_act = glu_act;
+  p.glu_limit = glu_limit;
   CUtensorMap mw, mx;
   if (dual && M > TILE_N && g_pair_kernel && n_ctas >= 2 && ((uintptr_t)out & 15) == 0 && ldo % 8 == 0) {
     // Two products of many tokens: the pair kernel computes them as one product whose weight
@@ -1692,11 +1699,11 @@ FERRUM_API int ferrum_gemm_tc_grouped_supported(const void* x, const void* w, in
 }
 
 // x [x_rows, ldx] (the first n_rows sorted by expert), w [n_exp, w_rows, K] dense, counts [n_exp] on the device.
-// glu: 0 float32 rows out [n_rows, ldo]; 1 / 2: silu / gelu_tanh of the gate rows times the up rows (rows N + n), out in the
-// operands' type.
+// glu: 0 float32 rows out [n_rows, ldo]; 1 / 2: silu / gelu_tanh of the gate rows times the up rows (rows N + n), 3: the
+// clamped unit of both with glu_limit; out in the operands' type.
 FERRUM_API int ferrum_gemm_tc_grouped(const void* x, const void* w, void* out, int dtype, int n_rows, int x_rows, int N, int K,
                                       int ldx, int ldo, int n_exp, int w_rows, const int* counts, int glu, int* err_flag,
-                                      cudaStream_t stream) {
+                                      float glu_limit, cudaStream_t stream) {
   FERRUM_CHECK_ARG(n_rows >= 0 && N > 0 && K > 0 && n_exp > 0, "gemm_tc_grouped: bad sizes");
   FERRUM_CHECK_ARG(ferrum_is_16bit(dtype), "gemm_tc_grouped: dtype code %d is not a 16-bit type", dtype);
   FERRUM_CHECK_ARG(err_flag != nullptr && counts != nullptr, "gemm_tc_grouped: the error flag and the counters are required");
@@ -1709,7 +1716,8 @@ FERRUM_API int ferrum_gemm_tc_grouped(const void* x, const void* w, void* out, i
   p.half = dtype == FERRUM_F16;
   p.wait_cycles = g_wait_cycles;
   p.drop_loads = g_drop_loads;
-  p.glu_act = glu == 2 ? 1 : 0;
+  p.glu_act = glu > 0 ? glu - 1 : 0;
+  p.glu_limit = glu_limit;
   GroupedParams g{counts, n_exp, w_rows};
   CUtensorMap mw, mx;
   if (int r = get_tensor_map(w, (long long)n_exp * w_rows, K, K, TILE_N, &mw)) return r;

@@ -3,6 +3,10 @@
 // moe_route   one warp per token: scores from the router's float32 logits (sigmoid of each, or a
 //             softmax over all), the `top` largest (ties: the lower index), optionally renormalised to
 //             sum 1; the token takes a place in each chosen expert's group (an atomic counter per expert).
+//             A correction vector may be added to the scores for the choice alone (the weights stay the
+//             plain scores), the weights may be multiplied by a constant, and the last router outputs may
+//             be identity experts (numbers n_real .. n_exp - 1: no matrices, no rows in the sorted buffer;
+//             the consumer adds weight * the token's own input for them).
 // moe_gather  one block per (token, choice): the token's input row, multiplied by the choice's weight
 //             where the design scales the expert's INPUT, goes to its place in a buffer sorted by
 //             expert (row = first row of the expert's group + the place taken above).
@@ -27,7 +31,8 @@ constexpr int MOE_MAX_TOP = 8;
 // logits [T][ldz] float32.  expert_of, rank_of [T*top] int32, weight_of [T*top] float32, counts [n_exp] (zero on entry).
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const float* __restrict__ logits, int ldz, int n_tokens, int n_exp, int top, int softmax_scores, int renormalize,
-                 int* __restrict__ expert_of, int* __restrict__ rank_of, float* __restrict__ weight_of, int* __restrict__ counts) {
+                 int* __restrict__ expert_of, int* __restrict__ rank_of, float* __restrict__ weight_of, int* __restrict__ counts,
+                 const float* __restrict__ correction, float weight_scale, int n_real) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x * 4 + warp;
   if (t >= n_tokens) return;
@@ -57,47 +62,57 @@ moe_route_kernel(const float* __restrict__ logits, int ldz, int n_tokens, int n_
     for (int i = 0; i < PER; ++i)
       if (lane + 32 * i < n_exp) s[i] = 1.f / (1.f + expf(-s[i]));
   }
+  float pick[PER];                          // what the choice goes by: the score, plus the correction when there is one
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int e = lane + 32 * i;
+    pick[i] = (correction != nullptr && e < n_exp) ? s[i] + correction[e] : s[i];
+  }
   float chosen_w[MOE_MAX_TOP];
   int chosen_e[MOE_MAX_TOP];
   float total = 0.f;
   for (int j = 0; j < top; ++j) {
-    float best = -INFINITY;
+    float best = -INFINITY, best_s = 0.f;
     int best_e = 0x7fffffff;
 #pragma unroll
     for (int i = 0; i < PER; ++i) {
       const int e = lane + 32 * i;
-      if (e < n_exp && s[i] > best) {       // (ascending e within a lane: the lower index wins a tie)
-        best = s[i];
+      if (e < n_exp && pick[i] > best) {    // (ascending e within a lane: the lower index wins a tie)
+        best = pick[i];
+        best_s = s[i];
         best_e = e;
       }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
       const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const float os = __shfl_xor_sync(0xffffffffu, best_s, o);
       const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
       if (ob > best || (ob == best && oe < best_e)) {
         best = ob;
+        best_s = os;
         best_e = oe;
       }
     }
-    chosen_w[j] = best;
+    chosen_w[j] = best_s;
     chosen_e[j] = best_e;
-    total += best;
+    total += best_s;
 #pragma unroll
     for (int i = 0; i < PER; ++i)
-      if (lane + 32 * i == best_e) s[i] = -INFINITY;
+      if (lane + 32 * i == best_e) pick[i] = -INFINITY;
   }
   if (lane == 0) {
     for (int j = 0; j < top; ++j) {
       const int e = chosen_e[j] < n_exp ? chosen_e[j] : 0;      // (all scores NaN: expert 0 with a NaN weight)
       expert_of[(size_t)t * top + j] = e;
-      weight_of[(size_t)t * top + j] = renormalize ? chosen_w[j] / total : chosen_w[j];
-      rank_of[(size_t)t * top + j] = atomicAdd(&counts[e], 1);
+      weight_of[(size_t)t * top + j] = (renormalize ? chosen_w[j] / total : chosen_w[j]) * weight_scale;
+      rank_of[(size_t)t * top + j] = e < n_real ? atomicAdd(&counts[e], 1) : 0;      // (an identity expert keeps no rows)
     }
   }
 }
 
-// x [T][ldx] -> xg [row][E] at the pair's place; row_of[pair] = row.  scale_input: the row is multiplied by the weight.
+// x [T][ldx] -> xg [row][E] at the pair's place; row_of[pair] = row (-1 for an identity expert, which has no row).
+// scale_input: the row is multiplied by the weight.
 template <typename T>
 __global__ void __launch_bounds__(128)
 moe_gather_kernel(const T* __restrict__ x, int ldx, int E, int n_exp, int top, const int* __restrict__ expert_of,
@@ -108,12 +123,13 @@ moe_gather_kernel(const T* __restrict__ x, int ldx, int E, int n_exp, int top, c
   if (threadIdx.x == 0) {
     const int e = expert_of[pair];
     int first = 0;
-    for (int i = 0; i < e; ++i) first += counts[i];
-    sm_row = first + rank_of[pair];
+    for (int i = 0; i < e && i < n_exp; ++i) first += counts[i];
+    sm_row = e < n_exp ? first + rank_of[pair] : -1;
     row_of[pair] = sm_row;
   }
   __syncthreads();
   const int row = sm_row;
+  if (row < 0) return;
   const float w = scale_input ? weight_of[pair] : 1.f;
   const T* src = x + (size_t)(pair / top) * ldx;
   T* dst = xg + (size_t)row * E;
@@ -125,6 +141,11 @@ __device__ __forceinline__ float moe_act(float z, int act) {
   if (act == 1) return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
   return z / (1.f + expf(-z));
 }
+// What the gated epilogue stores for a gate value and an up value (act 2: the clamped unit of common.cuh).
+__device__ __forceinline__ float moe_glu(float g, float u, int act, float limit) {
+  if (act == GLU_SWISH_CLAMP) return glu_swish_clamp(g, u, limit);
+  return moe_act(g, act) * u;
+}
 
 // A [rows][lda]; W [n_exp][w_rows][K]; counts [n_exp].  GLU: out[row][n] = act(C[row][n]) * C[row][F + n] in T (N = F);
 // else out[row][n] = C[row][n] in float32.  BM x BN outputs per CTA, K in steps of BK
@@ -132,7 +153,7 @@ __device__ __forceinline__ float moe_act(float z, int act) {
 template <typename T, int BM, bool GLU>
 __global__ void __launch_bounds__(256)
 moe_gemm_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, int w_rows, int K, int N, int n_exp,
-                const int* __restrict__ counts, int act, void* __restrict__ out, int ldo) {
+                const int* __restrict__ counts, int act, float limit, void* __restrict__ out, int ldo) {
   constexpr int BN = 64, BK = 16;
   constexpr int TM = BM / 16, TN = 4;             // 16 x 16 threads
   __shared__ float sa[BK][BM + 1];
@@ -210,7 +231,7 @@ moe_gemm_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, int w
     for (int j = 0; j < TN; ++j) {
       const int n = n0 + tx * TN + j;
       if (n >= N) continue;
-      if (GLU) reinterpret_cast<T*>(out)[row * ldo + n] = from_f32<T>(moe_act(acc[0][i][j], act) * acc[1][i][j]);
+      if (GLU) reinterpret_cast<T*>(out)[row * ldo + n] = from_f32<T>(moe_glu(acc[0][i][j], acc[1][i][j], act, limit));
       else reinterpret_cast<float*>(out)[row * ldo + n] = acc[0][i][j];
     }
   }
@@ -227,7 +248,7 @@ constexpr int MS_ROWS = 16, MS_WARPS = 8;
 template <typename T, bool GLU, bool VEC>
 __global__ void __launch_bounds__(MS_WARPS * 32)
 moe_gemm_skinny_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, int w_rows, int K, int N, int n_exp,
-                       const int* __restrict__ counts, int act, void* __restrict__ out, int ldo) {
+                       const int* __restrict__ counts, int act, float limit, void* __restrict__ out, int ldo) {
   __shared__ int tile_e, tile_row0, tile_rows;
   if (threadIdx.x == 0) {
     int left = blockIdx.x, first = 0, e = 0, rows = 0, row0 = 0;
@@ -301,7 +322,7 @@ moe_gemm_skinny_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W
   }
   if (lane < rows) {
     const size_t o = (size_t)(row0 + lane) * ldo + n;
-    if (GLU) reinterpret_cast<T*>(out)[o] = from_f32<T>(moe_act(r0, act) * r1);
+    if (GLU) reinterpret_cast<T*>(out)[o] = from_f32<T>(moe_glu(r0, r1, act, limit));
     else reinterpret_cast<float*>(out)[o] = r0;
   }
 }
@@ -356,7 +377,7 @@ constexpr int smem_bytes() { return STAGES * (BM + (GLU ? 2 : 1) * BN) * BK * 2;
 template <typename T, int BM, int BN, int WM, int WN, int STAGES, bool GLU>
 __global__ void __launch_bounds__(WM * WN * 32)
 moe_gemm_mma_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, int w_rows, int K, int N, int n_exp,
-                    const int* __restrict__ counts, int act, void* __restrict__ out, int ldo) {
+                    const int* __restrict__ counts, int act, float limit, void* __restrict__ out, int ldo) {
   constexpr int NT = WM * WN * 32;
   constexpr int NB = GLU ? 2 : 1;
   constexpr int MI = BM / WM / 16, NI = BN / WN / 8;
@@ -500,14 +521,14 @@ moe_gemm_mma_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, i
         for (int c = 0; c < 2; ++c) {
           const int n = n0 + wn * (NI * 8) + j * 8 + (lane & 3) * 2 + c;
           if (n >= N) continue;
-          if (GLU) reinterpret_cast<T*>(out)[o + n] = from_f32<T>(moe_act(acc[0][i][j][h * 2 + c], act) * acc[NB - 1][i][j][h * 2 + c]);
+          if (GLU) reinterpret_cast<T*>(out)[o + n] = from_f32<T>(moe_glu(acc[0][i][j][h * 2 + c], acc[NB - 1][i][j][h * 2 + c], act, limit));
           else reinterpret_cast<float*>(out)[o + n] = acc[0][i][j][h * 2 + c];
         }
     }
 }
 
 template <typename T, int BM, int BN, int WM, int WN, int STAGES, bool GLU>
-int launch(const T* A, int lda, const T* W, int w_rows, int K, int N, int n_exp, const int* counts, int n_rows, int act, void* out,
+int launch(const T* A, int lda, const T* W, int w_rows, int K, int N, int n_exp, const int* counts, int n_rows, int act, float limit, void* out,
            int ldo, cudaStream_t stream) {
   constexpr int smem = smem_bytes<BM, BN, STAGES, GLU>();
   static bool configured = false;
@@ -517,39 +538,45 @@ int launch(const T* A, int lda, const T* W, int w_rows, int K, int N, int n_exp,
     configured = true;
   }
   const dim3 grid((n_rows + BM - 1) / BM + n_exp, (N + BN - 1) / BN);
-  moe_gemm_mma_kernel<T, BM, BN, WM, WN, STAGES, GLU><<<grid, WM * WN * 32, smem, stream>>>(A, lda, W, w_rows, K, N, n_exp, counts, act, out, ldo);
+  moe_gemm_mma_kernel<T, BM, BN, WM, WN, STAGES, GLU><<<grid, WM * WN * 32, smem, stream>>>(A, lda, W, w_rows, K, N, n_exp, counts, act, limit, out, ldo);
   FERRUM_CHECK_LAUNCH("moe_gemm (tensor cores)");
   return 0;
 }
 
 template <typename T>
-int run(const void* A, int lda, const void* W, int w_rows, int K, int N, int n_exp, const int* counts, int n_rows, int glu, int act,
+int run(const void* A, int lda, const void* W, int w_rows, int K, int N, int n_exp, const int* counts, int n_rows, int glu, int act, float limit,
         void* out, int ldo, cudaStream_t stream) {
   const T* a = (const T*)A;
   const T* w = (const T*)W;
   const bool few = n_rows <= 32 * n_exp;        // about 32 rows an expert or fewer: tiles of 16 rows that stream the weights
   if (few) {
-    if (glu) return launch<T, 16, 64, 1, 4, 4, true>(a, lda, w, w_rows, K, N, n_exp, counts, n_rows, act, out, ldo, stream);
-    return launch<T, 16, 64, 1, 4, 4, false>(a, lda, w, w_rows, K, N, n_exp, counts, n_rows, act, out, ldo, stream);
+    if (glu) return launch<T, 16, 64, 1, 4, 4, true>(a, lda, w, w_rows, K, N, n_exp, counts, n_rows, act, limit, out, ldo, stream);
+    return launch<T, 16, 64, 1, 4, 4, false>(a, lda, w, w_rows, K, N, n_exp, counts, n_rows, act, limit, out, ldo, stream);
   }
-  if (glu) return launch<T, 128, 64, 4, 2, 3, true>(a, lda, w, w_rows, K, N, n_exp, counts, n_rows, act, out, ldo, stream);
-  return launch<T, 128, 128, 4, 2, 3, false>(a, lda, w, w_rows, K, N, n_exp, counts, n_rows, act, out, ldo, stream);
+  if (glu) return launch<T, 128, 64, 4, 2, 3, true>(a, lda, w, w_rows, K, N, n_exp, counts, n_rows, act, limit, out, ldo, stream);
+  return launch<T, 128, 128, 4, 2, 3, false>(a, lda, w, w_rows, K, N, n_exp, counts, n_rows, act, limit, out, ldo, stream);
 }
 
 }  // namespace moe_mma
 
 // y[t][:] = sum over the token's choices, in their order, of rows[row_of[t*top + j]][:] (float32), each times
-// weight_of[t*top + j] when that is given; for consumers that want a plain buffer.
+// weight_of[t*top + j] when that is given; for consumers that want a plain buffer.  A choice without a row
+// (row_of < 0: an identity expert) stands for the token's own input row x[t][:]; `add` (float32 rows, may be null:
+// a unit that every token runs through) joins the sum last.
+template <typename T>
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const float* __restrict__ rows, int ld, const int* __restrict__ row_of, const float* __restrict__ weight_of,
-                   int top, int E, float* __restrict__ y) {
+                   int top, int E, float* __restrict__ y, const T* __restrict__ x, int ldx, const float* __restrict__ add,
+                   int ld_add) {
   const int t = blockIdx.x;
   for (int i = threadIdx.x; i < E; i += 256) {
     float s = 0.f;
     for (int j = 0; j < top; ++j) {
-      const float v = rows[(size_t)row_of[(size_t)t * top + j] * ld + i];
+      const int r = row_of[(size_t)t * top + j];
+      const float v = r >= 0 ? rows[(size_t)r * ld + i] : (x != nullptr ? to_f32<T>(x[(size_t)t * ldx + i]) : 0.f);
       s += weight_of != nullptr ? v * weight_of[(size_t)t * top + j] : v;
     }
+    if (add != nullptr) s += add[(size_t)t * ld_add + i];
     y[(size_t)t * E + i] = s;
   }
 }
@@ -567,18 +594,22 @@ FERRUM_API int ferrum_moe_max_top() { return MOE_MAX_TOP; }
 // Routing and gathering of one step.  counts: n_exp ints (zeroed here).
 FERRUM_API int ferrum_moe_route(const float* logits, int ldz, int n_tokens, int n_exp, int top, int softmax_scores,
                                 int renormalize, const void* x, int ldx, int E, int dtype, int scale_input, int* expert_of,
-                                int* rank_of, float* weight_of, int* counts, void* xg, int* row_of, cudaStream_t stream) {
+                                int* rank_of, float* weight_of, int* counts, void* xg, int* row_of, const float* correction,
+                                float weight_scale, int n_identity, cudaStream_t stream) {
   FERRUM_CHECK_ARG(n_exp > 0 && n_exp <= MOE_MAX_EXPERTS && top > 0 && top <= MOE_MAX_TOP && top <= n_exp,
                    "moe_route: %d experts, %d per token are outside the kernel's limits (%d, %d)", n_exp, top, MOE_MAX_EXPERTS, MOE_MAX_TOP);
+  FERRUM_CHECK_ARG(n_identity >= 0 && n_identity < n_exp, "moe_route: %d identity experts among %d router outputs", n_identity, n_exp);
+  FERRUM_CHECK_ARG(n_identity == 0 || !scale_input, "moe_route: identity experts go with weights on the experts' results");
+  const int n_real = n_exp - n_identity;
   FERRUM_CHECK_ARG(ldz >= n_exp && ldx >= E && E > 0, "moe_route: rows are shorter than their contents");
   if (n_tokens == 0) return 0;
-  cudaError_t e = cudaMemsetAsync(counts, 0, sizeof(int) * n_exp, stream);
+  cudaError_t e = cudaMemsetAsync(counts, 0, sizeof(int) * n_real, stream);
   FERRUM_CHECK_ARG(e == cudaSuccess, "moe_route: cannot clear the counters: %s", cudaGetErrorString(e));
   moe_route_kernel<<<(n_tokens + 3) / 4, 128, 0, stream>>>(logits, ldz, n_tokens, n_exp, top, softmax_scores, renormalize,
-                                                           expert_of, rank_of, weight_of, counts);
+                                                           expert_of, rank_of, weight_of, counts, correction, weight_scale, n_real);
   FERRUM_CHECK_LAUNCH("moe_route");
   FERRUM_DISPATCH_DTYPE(dtype, T, (moe_gather_kernel<T><<<n_tokens * top, 128, 0, stream>>>(
-      (const T*)x, ldx, E, n_exp, top, expert_of, rank_of, weight_of, counts, scale_input, (T*)xg, row_of)));
+      (const T*)x, ldx, E, n_real, top, expert_of, rank_of, weight_of, counts, scale_input, (T*)xg, row_of)));
   FERRUM_CHECK_LAUNCH("moe_gather");
   return 0;
 }
@@ -586,7 +617,7 @@ FERRUM_API int ferrum_moe_route(const float* logits, int ldz, int n_tokens, int 
 // n_rows: the sorted rows (tokens x top).  glu != 0: W holds gate rows 0..N-1 and up rows N..2N-1 per expert
 // (w_rows = 2N), out is [n_rows][ldo] in the compute type; else out is float32.
 FERRUM_API int ferrum_moe_gemm(const void* A, int lda, const void* W, int w_rows, int K, int N, int n_exp, const int* counts,
-                               int n_rows, int dtype, int glu, int act, void* out, int ldo, cudaStream_t stream) {
+                               int n_rows, int dtype, int glu, int act, float limit, void* out, int ldo, cudaStream_t stream) {
   FERRUM_CHECK_ARG(K > 0 && N > 0 && lda >= K && ldo >= N && w_rows >= (glu ? 2 * N : N), "moe_gemm: shapes do not agree");
   FERRUM_CHECK_ARG(n_exp > 0 && n_exp <= MOE_MAX_EXPERTS, "moe_gemm: bad number of experts %d", n_exp);
   if (n_rows == 0) return 0;
@@ -595,15 +626,15 @@ FERRUM_API int ferrum_moe_gemm(const void* A, int lda, const void* W, int w_rows
   if (dtype != FERRUM_F32 && !g_moe_cuda_cores && K % 8 == 0 && lda % 8 == 0 && (reinterpret_cast<uintptr_t>(A) & 15) == 0 &&
       (reinterpret_cast<uintptr_t>(W) & 15) == 0) {
     if (dtype == FERRUM_BF16)
-      return moe_mma::run<__nv_bfloat16>(A, lda, W, w_rows, K, N, n_exp, counts, n_rows, glu, act, out, ldo, stream);
-    if (dtype == FERRUM_F16) return moe_mma::run<__half>(A, lda, W, w_rows, K, N, n_exp, counts, n_rows, glu, act, out, ldo, stream);
+      return moe_mma::run<__nv_bfloat16>(A, lda, W, w_rows, K, N, n_exp, counts, n_rows, glu, act, limit, out, ldo, stream);
+    if (dtype == FERRUM_F16) return moe_mma::run<__half>(A, lda, W, w_rows, K, N, n_exp, counts, n_rows, glu, act, limit, out, ldo, stream);
   }
 #define MT_LAUNCH(BM)                                                                                                  \
   do {                                                                                                                 \
     if (glu) FERRUM_DISPATCH_DTYPE(dtype, T, (moe_gemm_kernel<T, BM, true><<<grid, 256, 0, stream>>>(                   \
-        (const T*)A, lda, (const T*)W, w_rows, K, N, n_exp, counts, act, out, ldo)));                                  \
+        (const T*)A, lda, (const T*)W, w_rows, K, N, n_exp, counts, act, limit, out, ldo)));                                  \
     else FERRUM_DISPATCH_DTYPE(dtype, T, (moe_gemm_kernel<T, BM, false><<<grid, 256, 0, stream>>>(                      \
-        (const T*)A, lda, (const T*)W, w_rows, K, N, n_exp, counts, act, out, ldo)));                                  \
+        (const T*)A, lda, (const T*)W, w_rows, K, N, n_exp, counts, act, limit, out, ldo)));                                  \
   } while (0)
   if (n_rows <= 32 * n_exp) {         // about 32 rows an expert or fewer: a stream of the weights
     const dim3 grid((n_rows + MS_ROWS - 1) / MS_ROWS + n_exp, (N + MS_WARPS - 1) / MS_WARPS);
@@ -612,7 +643,7 @@ FERRUM_API int ferrum_moe_gemm(const void* A, int lda, const void* W, int w_rows
                      (reinterpret_cast<uintptr_t>(W) & 15) == 0;
 #define MS_LAUNCH(T, G, V)                                                                                                   \
   moe_gemm_skinny_kernel<T, G, V><<<grid, MS_WARPS * 32, 0, stream>>>((const T*)A, lda, (const T*)W, w_rows, K, N, n_exp, counts, \
-                                                                      act, out, ldo)
+                                                                      act, limit, out, ldo)
     if (vec) {
       if (glu) MS_LAUNCH(float, true, true);
       else MS_LAUNCH(float, false, true);
@@ -638,10 +669,13 @@ FERRUM_API int ferrum_moe_gemm(const void* A, int lda, const void* W, int w_rows
 }
 
 FERRUM_API int ferrum_moe_combine(const float* rows, int ld, const int* row_of, const float* weight_of, int top, int n_tokens,
-                                  int E, float* y, cudaStream_t stream) {
+                                  int E, float* y, const void* x, int ldx, int x_dtype, const float* add, int ld_add,
+                                  cudaStream_t stream) {
   FERRUM_CHECK_ARG(top > 0 && E > 0 && ld >= E, "moe_combine: bad sizes");
+  FERRUM_CHECK_ARG((x == nullptr || ldx >= E) && (add == nullptr || ld_add >= E), "moe_combine: a row is shorter than the width");
   if (n_tokens == 0) return 0;
-  moe_combine_kernel<<<n_tokens, 256, 0, stream>>>(rows, ld, row_of, weight_of, top, E, y);
+  FERRUM_DISPATCH_DTYPE(x_dtype, T, (moe_combine_kernel<T><<<n_tokens, 256, 0, stream>>>(rows, ld, row_of, weight_of, top, E, y,
+                                                                                       (const T*)x, ldx, add, ld_add)));
   FERRUM_CHECK_LAUNCH("moe_combine");
   return 0;
 }

@@ -22,11 +22,11 @@ _DT = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
 SIXTEEN_BIT = (torch.bfloat16, torch.float16)       # the tensor-core kernels take either
 
 EPI_STORE, EPI_STORE_F32, EPI_RESIDUAL = 0, 1, 2                       # generic product
-TC_STORE_BF16, TC_STORE_F32, TC_RESIDUAL, TC_SWIGLU, TC_GEGLU = 0, 1, 2, 3, 4       # tcgen05 product (GEGLU: SWIGLU with gelu_tanh on the gate)
+TC_STORE_BF16, TC_STORE_F32, TC_RESIDUAL, TC_SWIGLU, TC_GEGLU, TC_SWISH_CLAMP = 0, 1, 2, 3, 4, 5   # tcgen05 product (GEGLU: SWIGLU with gelu_tanh on the gate; SWISH_CLAMP: the clamped unit)
 
 _lib = None
 _lock = threading.Lock()
-ABI = 16
+ABI = 17
 
 
 def lib():
@@ -342,7 +342,7 @@ def gemm_tc_workspace(M, N, K, dual, n_ctas=0):
     return int(need), tiles.value
 
 
-def gemm_tc(x, w, out, epilogue, err, workspace, counters, M=None, N=None, dual_offset=0, n_ctas=0):
+def gemm_tc(x, w, out, epilogue, err, workspace, counters, M=None, N=None, dual_offset=0, n_ctas=0, glu_limit=0.0):
     """16-bit (bfloat16 or float16) tensor-core product; see csrc/kernels/gemm_tc.cu.  `N` is the number of
     output features (rows of w used per product); with dual_offset > 0 rows dual_offset + n
     feed the second product of the SwiGLU epilogue.  `workspace` (float32) and `counters`
@@ -354,7 +354,7 @@ def gemm_tc(x, w, out, epilogue, err, workspace, counters, M=None, N=None, dual_
     N = (w.shape[0] - dual_offset) if N is None else N
     if x.shape[1] != K or out.shape[1] < N or out.shape[0] < M or x.shape[0] < M:
         raise KernelError(f"gemm_tc: shapes do not agree: x {tuple(x.shape)} w {tuple(w.shape)} out {tuple(out.shape)}")
-    want = x.dtype if epilogue in (TC_STORE_BF16, TC_SWIGLU, TC_GEGLU) else torch.float32
+    want = x.dtype if epilogue in (TC_STORE_BF16, TC_SWIGLU, TC_GEGLU, TC_SWISH_CLAMP) else torch.float32
     if out.dtype != want:
         raise KernelError(f"gemm_tc: out must be {want} for epilogue {epilogue}")
     _need(workspace, torch.float32, "workspace")
@@ -363,7 +363,7 @@ def gemm_tc(x, w, out, epilogue, err, workspace, counters, M=None, N=None, dual_
     _check(lib().ferrum_gemm_tc(_ptr(x), _ptr(w), _ptr(out), dtype_code(x.dtype), c_int(M), c_int(N), c_int(K), c_int(x.stride(0)),
                                 c_int(w.stride(0)), c_int(out.stride(0)), c_int(w.shape[0]), c_int(epilogue),
                                 c_int(dual_offset), c_int(n_ctas), _ptr(workspace), c_longlong(workspace.numel()),
-                                _ptr(counters), c_int(counters.numel()), _ptr(err), _stream()), "gemm_tc")
+                                _ptr(counters), c_int(counters.numel()), _ptr(err), c_float(glu_limit), _stream()), "gemm_tc")
 
 
 def rope_cache_write(qkv, n_tokens, positions, req_of_token, block_table, cos_sin, kv_plane, page_stride, page_size,
@@ -401,7 +401,7 @@ def attention_generic_split():
 
 def attention_generic(q, out, n_tokens, positions, req_of_token, block_table, kv_plane, page_stride, page_size, Hq,
                       Hkv, D, scale, window, err, part=None, split_slots=0, q_start=None, n_reqs=0, distance_penalty=None,
-                      chunked=False):
+                      chunked=False, softcap=0.0, sink=False):
     """Causal GQA attention of every token over its request's pages on the CUDA cores, float32
     arithmetic.  part=None: one CTA per (token, group of heads) walks the whole key range (many
     tokens).  With `part` (float32, n_tokens * Hq * split_slots * (D + 2) elements) every row's keys
@@ -412,7 +412,8 @@ def attention_generic(q, out, n_tokens, positions, req_of_token, block_table, kv
     distance_penalty=(r1, r2), float32 per query head: r1[h] * ln(1 + r2[h] * (position - key position))
     is taken off the scaled score; with r2 None it is the straight line r1[h] * (position - key position).
     chunked: `window` is the length of a chunk (positions are cut into chunks from 0; a query sees its own
-    chunk's keys up to itself) instead of a sliding window.  `out` may be float32 whatever the cache's type
+    chunk's keys up to itself) instead of a sliding window.  softcap c > 0: the scaled score becomes c * tanh(score / c).
+    sink: a key of score 0 without a value joins every softmax (one more term in its denominator).  `out` may be float32 whatever the cache's type
     (a kernel after this one still works on the heads' results)."""
     _need(q, None, "q", 2); _need(out, None, "out", 2); _need(kv_plane, q.dtype, "kv_plane")
     if out.dtype not in (q.dtype, torch.float32):
@@ -440,7 +441,7 @@ def attention_generic(q, out, n_tokens, positions, req_of_token, block_table, kv
                                           c_float(scale), c_int(window), _ptr(err), _ptr(part), c_int(split_slots),
                                           _ptr(q_start) if part is None else None, c_int(n_reqs), _ptr(r1), _ptr(r2),
                                           c_int(1 if out.dtype == torch.float32 and q.dtype != torch.float32 else 0),
-                                          c_int(1 if chunked else 0), _stream()),
+                                          c_int(1 if chunked else 0), c_float(softcap or 0.0), c_int(1 if sink else 0), _stream()),
            "attention_generic")
 
 
@@ -575,10 +576,10 @@ def norm_pair_shift(x, w1, w2, shift, a, m, b, n_tokens, ctx, state, stage, grou
                                         _stream()), "norm_pair_shift")
 
 
-GLU_ACTS = {"silu": 0, "gelu_tanh": 1}
+GLU_ACTS = {"silu": 0, "gelu_tanh": 1, "swish_clamp": 2}      # swish_clamp: min(g, L) sigmoid(1.702 min(g, L)) (clamp(u, -L, L) + 1)
 
 
-def bias_glu(gu, bias_gate, bias_up, act, n_tokens, F, kind="silu"):
+def bias_glu(gu, bias_gate, bias_up, act, n_tokens, F, kind="silu", limit=0.0):
     """act[t, f] = f(gu[t, f] + bias_gate[f]) * (gu[t, F + f] + bias_up[f]); gu float32."""
     _need(gu, torch.float32, "gu", 2); _need(act, None, "act", 2)
     for bias in (bias_gate, bias_up):
@@ -588,10 +589,10 @@ def bias_glu(gu, bias_gate, bias_up, act, n_tokens, F, kind="silu"):
     if _profile is not None:
         _work = (n_tokens * F * (8 + act.element_size()), 0.0)
     _check(lib().ferrum_bias_glu(_ptr(gu), c_int(gu.stride(0)), _ptr(bias_gate), _ptr(bias_up), _ptr(act), dtype_code(act.dtype),
-                                 c_int(act.stride(0)), c_int(n_tokens), c_int(F), c_int(GLU_ACTS[kind]), _stream()), "bias_glu")
+                                 c_int(act.stride(0)), c_int(n_tokens), c_int(F), c_int(GLU_ACTS[kind]), c_float(limit), _stream()), "bias_glu")
 
 
-def bias_glu_reduce(partials, bias_gate, bias_up, act, n_tokens, F, kind="silu", extra=None):
+def bias_glu_reduce(partials, bias_gate, bias_up, act, n_tokens, F, kind="silu", extra=None, limit=0.0):
     """`bias_glu` on a product of 2F + n rows (gate | up | extra) that was left in deferred mode; the n
     extra columns are summed into `extra` (float32 [T, n], contiguous)."""
     _need(act, None, "act", 2)
@@ -602,7 +603,7 @@ def bias_glu_reduce(partials, bias_gate, bias_up, act, n_tokens, F, kind="silu",
             raise KernelError("bias_glu_reduce: extra must be contiguous")
         n_extra = extra.shape[1]
     _check(lib().ferrum_bias_glu_reduce(_ptr(bias_gate), _ptr(bias_up), _ptr(act), dtype_code(act.dtype), c_int(act.stride(0)),
-                                        c_int(n_tokens), c_int(F), c_int(GLU_ACTS[kind]), _ptr(extra), c_int(n_extra),
+                                        c_int(n_tokens), c_int(F), c_int(GLU_ACTS[kind]), c_float(limit), _ptr(extra), c_int(n_extra),
                                         _ptr(partials.workspace), partials._c, _stream()), "bias_glu_reduce")
 
 
@@ -765,7 +766,7 @@ def head_linear(x, x_head_stride, w, y, y_head_stride, n_tokens):
 # ----------------------------------------------------------------------------- shaped attention heads
 def qkv_shape(proj, n_tokens, ctx, block_table, rot, qk_pairing, value_rot, value_pairing, unit_norm, eps, q_out, plane,
               page_stride, page_size, Hq, Hkv, Dk, Dv, Dp, writes, bias=None, q_norm=None, k_norm=None, q_temp=None,
-              value_mix=None):
+              value_mix=None, whole_norm=False, value_from_key=False):
     """Per head of a float32 product row [q | k | v | ...]: rotary turn of q and k (table `rot`:
     `.cos_sin` [positions, R/2, 2], `.rope_dim`; None: none), optional division by the head's root
     mean square, a turn of the value over all its elements (`value_rot`: a table [positions, Dv/2, 2]
@@ -773,8 +774,10 @@ def qkv_shape(proj, n_tokens, ctx, block_table, rot, qk_pairing, value_rot, valu
     bias: float32 [Hq*Dk + Hkv*(Dk+Dv)] added first.  q_norm / k_norm: float32 [Dk] weights of an RMS norm
     of every query / key head before the turn.  q_temp = (coef, every): a query at position p is multiplied
     by 1 + coef * ln(floor((p + 1) / every) + 1).  value_mix = ("store", v_first) leaves the float32 values
-    in v_first [T, Hkv*Dv]; ("blend", v_first, lam) caches (1 - lam) v + lam v_first (lam: one float on the device)."""
-    for t, n in ((bias, Hq * Dk + Hkv * (Dk + Dv)), (q_norm, Dk), (k_norm, Dk)):
+    in v_first [T, Hkv*Dv]; ("blend", v_first, lam) caches (1 - lam) v + lam v_first (lam: one float on the device).
+    whole_norm: q_norm [Hq*Dk] and k_norm [Hkv*Dk] are the weights of an RMS norm over the token's whole query / key
+    projection (all heads at once).  value_from_key: the row is [q | k] and a KV head's value is its key as projected."""
+    for t, n in ((bias, Hq * Dk + Hkv * (Dk + Dv)), (q_norm, Hq * Dk if whole_norm else Dk), (k_norm, Hkv * Dk if whole_norm else Dk)):
         if t is not None:
             _need(t, torch.float32, "qkv_shape vector", 1)
             if t.shape[0] != n or not t.is_contiguous():
@@ -791,7 +794,7 @@ def qkv_shape(proj, n_tokens, ctx, block_table, rot, qk_pairing, value_rot, valu
             lam = value_mix[2]
             _need(lam, torch.float32, "lambda")
     _need(proj, torch.float32, "proj", 2); _need(q_out, plane.dtype, "q_out", 2); _need(block_table, torch.int32, "block_table", 2)
-    if proj.shape[1] < Hq * Dk + (Hkv * (Dk + Dv) if writes else 0) or q_out.shape[1] < Hq * Dp:
+    if proj.shape[1] < Hq * Dk + ((Hkv * Dk if value_from_key else Hkv * (Dk + Dv)) if writes else 0) or q_out.shape[1] < Hq * Dp:
         raise KernelError("qkv_shape: a row is too short for the heads")
     cs = rot.cos_sin if rot is not None else None
     _check(lib().ferrum_qkv_shape(_ptr(proj), c_int(proj.stride(0)), c_int(n_tokens), _ptr(ctx.positions), _ptr(ctx.req_of_token),
@@ -802,7 +805,8 @@ def qkv_shape(proj, n_tokens, ctx, block_table, rot, qk_pairing, value_rot, valu
                                   c_longlong(page_stride), c_int(page_size), dtype_code(plane.dtype), c_int(Hq), c_int(Hkv),
                                   c_int(Dk), c_int(Dv), c_int(Dp), c_int(1 if writes else 0), _ptr(ctx.err), _ptr(bias),
                                   _ptr(q_norm), _ptr(k_norm), c_float(coef), c_int(every), c_int(mode), _ptr(v_first),
-                                  c_int(v_first.stride(0) if v_first is not None else 0), _ptr(lam), _stream()),
+                                  c_int(v_first.stride(0) if v_first is not None else 0), _ptr(lam), c_int(1 if whole_norm else 0),
+                                  c_int(1 if value_from_key else 0), _stream()),
            "qkv_shape")
 
 
@@ -965,22 +969,29 @@ MOE_MAX_EXPERTS, MOE_MAX_TOP = 256, 8      # (the routing kernel's own limits, w
 
 
 def moe_route(logits, n_tokens, n_exp, top, x, scale_input, expert_of, rank_of, weight_of, counts, xg, row_of, scores="sigmoid",
-              renormalize=False):
+              renormalize=False, correction=None, weight_scale=1.0, n_identity=0):
     """From the router's float32 logits [T, >= n_exp]: every token's `top` experts and their weights, and the
     tokens' input rows x [T, E] gathered into xg [T * top, E] sorted by expert (times the weight when
-    `scale_input`); row_of [T * top] says where each (token, choice) went; counts [n_exp] the rows per expert."""
+    `scale_input`); row_of [T * top] says where each (token, choice) went; counts [n_exp] the rows per expert.
+    correction (float32 [n_exp]) is added to the scores for the choice only; the weights are the plain scores times
+    weight_scale.  The last n_identity of the n_exp router outputs are identity experts: they get no rows (row_of -1)."""
     global launches
     _need(logits, torch.float32, "logits", 2); _need(x, None, "x", 2); _need(xg, x.dtype, "xg", 2)
     for t in (expert_of, rank_of, counts, row_of):
         _need(t, torch.int32, "routing table")
     _need(weight_of, torch.float32, "weight_of")
     E = x.shape[1]
-    if xg.shape[1] != E or xg.shape[0] < n_tokens * top or not xg.is_contiguous() or counts.numel() < n_exp:
+    if xg.shape[1] != E or xg.shape[0] < n_tokens * top or not xg.is_contiguous() or counts.numel() < n_exp - n_identity:
         raise KernelError("moe_route: buffers are too small")
+    if correction is not None:
+        _need(correction, torch.float32, "correction", 1)
+        if correction.shape[0] != n_exp or not correction.is_contiguous():
+            raise KernelError("moe_route: the correction has one number per router output")
     _check(lib().ferrum_moe_route(_ptr(logits), c_int(logits.stride(0)), c_int(n_tokens), c_int(n_exp), c_int(top),
                                   c_int(MOE_SCORES[scores]), c_int(1 if renormalize else 0), _ptr(x), c_int(x.stride(0)), c_int(E),
                                   dtype_code(x.dtype), c_int(1 if scale_input else 0), _ptr(expert_of), _ptr(rank_of),
-                                  _ptr(weight_of), _ptr(counts), _ptr(xg), _ptr(row_of), _stream()), "moe_route")
+                                  _ptr(weight_of), _ptr(counts), _ptr(xg), _ptr(row_of), _ptr(correction), c_float(weight_scale),
+                                  c_int(n_identity), _stream()), "moe_route")
     launches += 1          # (the entry point launches the routing and the gather)
 
 
@@ -994,7 +1005,7 @@ def set_moe_tcgen05(on: bool):
     _moe_tcgen05 = bool(on)
 
 
-def moe_gemm(a, w, counts, n_rows, out, N, glu=None, err=None):
+def moe_gemm(a, w, counts, n_rows, out, N, glu=None, err=None, limit=0.0):
     """out[row] = a[row] @ w[expert of row].T over rows sorted by expert (`counts` rows each, on the device).
     w: [n_exp, rows, K]; glu ("silu" / "gelu_tanh"): w holds N gate rows then N up rows per expert and out
     (compute type) gets act(gate) * up; else out is float32 [n_rows, N].  With `err` (the step's error flag) 16-bit
@@ -1012,10 +1023,10 @@ def moe_gemm(a, w, counts, n_rows, out, N, glu=None, err=None):
             and lib().ferrum_gemm_tc_grouped_supported(_ptr(a), _ptr(w), c_int(n_rows), c_int(n_exp), c_int(K), c_int(a.stride(0)))):
         _check(lib().ferrum_gemm_tc_grouped(_ptr(a), _ptr(w), _ptr(out), dtype_code(a.dtype), c_int(n_rows), c_int(a.shape[0]), c_int(N),
                                             c_int(K), c_int(a.stride(0)), c_int(out.stride(0)), c_int(n_exp), c_int(w_rows), _ptr(counts),
-                                            c_int(1 + GLU_ACTS[glu] if glu else 0), _ptr(err), _stream()), "moe_gemm")
+                                            c_int(1 + GLU_ACTS[glu] if glu else 0), _ptr(err), c_float(limit), _stream()), "moe_gemm")
         return
     _check(lib().ferrum_moe_gemm(_ptr(a), c_int(a.stride(0)), _ptr(w), c_int(w_rows), c_int(K), c_int(N), c_int(n_exp), _ptr(counts),
-                                 c_int(n_rows), dtype_code(a.dtype), c_int(1 if glu else 0), c_int(GLU_ACTS[glu] if glu else 0),
+                                 c_int(n_rows), dtype_code(a.dtype), c_int(1 if glu else 0), c_int(GLU_ACTS[glu] if glu else 0), c_float(limit),
                                  _ptr(out), c_int(out.stride(0)), _stream()), "moe_gemm")
 
 
@@ -1024,17 +1035,133 @@ def set_moe_cuda_cores(on: bool):
     lib().ferrum_moe_cuda_cores(c_int(1 if on else 0))
 
 
-def moe_combine(rows, row_of, top, n_tokens, y, weight_of=None):
-    """y[t] = sum_j rows[row_of[t, j]] (times weight_of[t, j] when given), float32."""
+def moe_combine(rows, row_of, top, n_tokens, y, weight_of=None, x=None, add=None):
+    """y[t] = sum_j rows[row_of[t, j]] (times weight_of[t, j] when given), float32.  x [T, E] (any type): the tokens'
+    own input rows, which stand in for choices without a row (row_of < 0: identity experts); add (float32 [T, E]): rows
+    that join the sum last."""
     _need(rows, torch.float32, "rows", 2); _need(y, torch.float32, "y", 2); _need(row_of, torch.int32, "row_of")
     E = y.shape[1]
     if not y.is_contiguous() or rows.shape[1] < E:
         raise KernelError("moe_combine: shapes do not agree")
+    if x is not None:
+        _need(x, None, "x", 2)
+    if add is not None:
+        _need(add, torch.float32, "add", 2)
+    if (x is not None and x.shape[1] < E) or (add is not None and add.shape[1] < E):
+        raise KernelError("moe_combine: shapes do not agree")
     _check(lib().ferrum_moe_combine(_ptr(rows), c_int(rows.stride(0)), _ptr(row_of), _ptr(weight_of), c_int(top), c_int(n_tokens),
-                                    c_int(E), _ptr(y), _stream()), "moe_combine")
+                                    c_int(E), _ptr(y), _ptr(x), c_int(x.stride(0) if x is not None else 0),
+                                    dtype_code(x.dtype) if x is not None else c_int(F32), _ptr(add),
+                                    c_int(add.stride(0) if add is not None else 0), _stream()), "moe_combine")
 
 
 def softcap(x, n_rows, cap):
     """x[:n_rows] <- cap * tanh(x / cap) in place (float32)."""
     _need(x, torch.float32, "x", 2)
     _check(lib().ferrum_softcap(_ptr(x), c_int(x.stride(0)), c_int(n_rows), c_int(x.shape[1]), c_float(cap), _stream()), "softcap")
+
+
+# ----------------------------------------------------------------------------- norms on the sublayers' results
+def post_norm_add(h, n_tokens, y=None, w=None, ls=None, eps=0.0, xc=None):
+    """h[:n] += ls * (y / sqrt(mean(y^2) + eps) * w), all float32 (ls: a per-element layer scale or None); xc (a
+    compute-type buffer or None) receives the new rows.  Without y only that copy is made."""
+    _need(h, torch.float32, "h", 2)
+    E = h.shape[1]
+    if not h.is_contiguous():
+        raise KernelError("post_norm_add: the residual rows must be contiguous")
+    if y is not None:
+        _need(y, torch.float32, "y", 2); _need(w, torch.float32, "w", 1)
+        if y.shape[1] < E or w.shape[0] != E or (ls is not None and (ls.dtype != torch.float32 or ls.shape[0] != E)):
+            raise KernelError("post_norm_add: shapes do not agree")
+    if xc is not None:
+        _need(xc, None, "xc", 2)
+        if xc.shape[1] < E:
+            raise KernelError("post_norm_add: shapes do not agree")
+    _bytes_work((h, 2 * n_tokens), (y, n_tokens), (xc, n_tokens))
+    _check(lib().ferrum_post_norm_add(_ptr(h), c_int(E), _ptr(y), c_int(y.stride(0) if y is not None else 0), _ptr(w), _ptr(ls),
+                                      c_float(eps), _ptr(xc), c_int(xc.stride(0) if xc is not None else 0),
+                                      dtype_code(xc.dtype) if xc is not None else c_int(F32), c_int(n_tokens), _stream()),
+           "post_norm_add")
+
+
+def dual_norm_mean(a, b, wa, wb, eps, out, n_tokens):
+    """out[:n] = (rms(a) * wa + rms(b) * wb) / 2 with rms(v) = v / sqrt(mean(v^2) + eps), all float32 [T, E]."""
+    for t, n in ((a, "a"), (b, "b"), (out, "out")):
+        _need(t, torch.float32, n, 2)
+    E = out.shape[1]
+    _need(wa, torch.float32, "wa", 1); _need(wb, torch.float32, "wb", 1)
+    if a.shape[1] < E or b.shape[1] < E or wa.shape[0] != E or wb.shape[0] != E:
+        raise KernelError("dual_norm_mean: shapes do not agree")
+    _bytes_work((a, n_tokens), (b, n_tokens), (out, n_tokens))
+    _check(lib().ferrum_dual_norm_mean(_ptr(a), c_int(a.stride(0)), _ptr(b), c_int(b.stride(0)), _ptr(wa), _ptr(wb), c_float(eps),
+                                       c_int(E), _ptr(out), c_int(out.stride(0)), c_int(n_tokens), _stream()), "dual_norm_mean")
+
+
+def head_gate_norm(o, gate, w, eps, n_tokens, H, Dv, out):
+    """out[t, h] = rms(o[t, h]) * w * sigmoid(gate[t, h]) per head of Dv elements, rounded once to out's type.  o, gate:
+    float32 rows (gate may be a view into wider rows, or None); w: float32 [Dv] (one for all heads) or [H * Dv]."""
+    _need(o, torch.float32, "o", 2); _need(out, None, "out", 2); _need(w, torch.float32, "w", 1)
+    if gate is not None:
+        _need(gate, torch.float32, "gate", 2)
+    if w.shape[0] not in (Dv, H * Dv) or o.shape[1] < H * Dv or out.shape[1] < H * Dv:
+        raise KernelError("head_gate_norm: shapes do not agree")
+    _bytes_work((o, n_tokens), (gate, n_tokens), (out, n_tokens))
+    _check(lib().ferrum_head_gate_norm(_ptr(o), c_int(o.stride(0)), _ptr(gate), c_int(gate.stride(0) if gate is not None else 0),
+                                       _ptr(w), c_int(1 if w.shape[0] == H * Dv and H > 1 else 0), c_float(eps), c_int(n_tokens),
+                                       c_int(H), c_int(Dv), _ptr(out), c_int(out.stride(0)), dtype_code(out.dtype), _stream()),
+           "head_gate_norm")
+
+
+# ----------------------------------------------------------------------------- recurrent mixers with a matrix per head
+DELTA_MAX_TAPS, RECURRENT_MAX_DIM = 16, 256      # (the kernels' own limits, which they check again)
+
+
+def delta_rule(proj, logit, n_tokens, ctx, conv_w, dt_bias, a_log, H, G, D, Dv, state, qkv, dec, o):
+    """Everything of the gated delta rule between its products: short convolution + silu over q, k, v (its last
+    inputs kept in the request's state row), unit norm of q and k, the decays, the walk over the tokens.
+    proj: float32 rows [q: G D | k: G D | v: H Dv | beta logits: H]; logit: float32 rows [H D] (decay logits before
+    dt_bias); state: float32 [max_requests, H D Dv + (taps - 1) C]; qkv [T, C], dec [T, H D]: float32 scratch;
+    o: float32 [T, H Dv]."""
+    global launches
+    _need(proj, torch.float32, "proj", 2); _need(logit, torch.float32, "logit", 2); _need(state, torch.float32, "state", 2)
+    _need(o, torch.float32, "o", 2)
+    C = 2 * G * D + H * Dv
+    taps = conv_w.shape[1]
+    for t, n in ((conv_w, "conv_w"), (dt_bias, "dt_bias"), (a_log, "a_log")):
+        _need(t, torch.float32, n)
+    if (conv_w.shape[0] != C or not conv_w.is_contiguous() or dt_bias.numel() != H * D or a_log.numel() != H
+            or state.shape[1] != H * D * Dv + (taps - 1) * C or qkv.numel() < n_tokens * C or dec.numel() < n_tokens * H * D):
+        raise KernelError("delta_rule: shapes do not agree")
+    if _profile is not None:
+        global _work
+        _work = (4 * (n_tokens * (2 * C + 2 * H * D + H * Dv) + 2 * ctx.n_reqs * H * D * Dv), 6.0 * n_tokens * H * D * Dv)
+    _check(lib().ferrum_delta_rule(_ptr(proj), c_int(proj.stride(0)), _ptr(logit), c_int(logit.stride(0)), c_int(n_tokens),
+                                   c_int(ctx.n_reqs), _ptr(ctx.req_of_token), _ptr(ctx.q_start), _ptr(ctx.slots), _ptr(conv_w),
+                                   c_int(taps), _ptr(dt_bias), _ptr(a_log), c_int(H), c_int(G), c_int(D), c_int(Dv), _ptr(state),
+                                   c_longlong(state.stride(0)), _ptr(qkv), _ptr(dec), _ptr(o), c_int(o.stride(0)), _stream()),
+           "delta_rule")
+    launches += 2 if taps > 1 else 1       # (the entry point launches the preparation, the convolution's state and the walk)
+
+
+def matrix_memory_state_size(H, D, Dv):
+    """Floats of a request's state row: S [H, D, Dv] and, per block of 32 value columns, a copy of n [H, D] and m [H]."""
+    return H * D * Dv + ((Dv + 31) // 32) * (H * D + H)
+
+
+def matrix_memory(proj, offsets, bias_i, bias_f, cap, n_tokens, ctx, H, D, Dv, state, o):
+    """The walk of the matrix-memory recurrence (see csrc/kernels/matrix_memory.cu).  proj: float32 rows holding q, k,
+    v and the two gates' logits at `offsets` = (q, k, v, i, f); state: float32 [max_requests, matrix_memory_state_size];
+    o: float32 [T, H Dv]."""
+    _need(proj, torch.float32, "proj", 2); _need(state, torch.float32, "state", 2); _need(o, torch.float32, "o", 2)
+    _need(bias_i, torch.float32, "bias_i", 1); _need(bias_f, torch.float32, "bias_f", 1)
+    oq, ok, ov, oi, of = (int(v) for v in offsets)
+    if (bias_i.shape[0] != H or bias_f.shape[0] != H or state.shape[1] != matrix_memory_state_size(H, D, Dv)
+            or proj.shape[1] < max(oq + H * D, ok + H * D, ov + H * Dv, oi + H, of + H)):
+        raise KernelError("matrix_memory: shapes do not agree")
+    if _profile is not None:
+        global _work
+        _work = (4 * (n_tokens * (2 * H * D + 2 * H * Dv) + 2 * ctx.n_reqs * H * D * Dv), 4.0 * n_tokens * H * D * Dv)
+    _check(lib().ferrum_matrix_memory(_ptr(proj), c_int(proj.stride(0)), c_int(oq), c_int(ok), c_int(ov), c_int(oi), c_int(of),
+                                      _ptr(bias_i), _ptr(bias_f), c_float(cap), c_int(n_tokens), c_int(ctx.n_reqs), _ptr(ctx.q_start),
+                                      _ptr(ctx.slots), c_int(H), c_int(D), c_int(Dv), _ptr(state), c_longlong(state.stride(0)),
+                                      _ptr(o), c_int(o.stride(0)), _stream()), "matrix_memory")

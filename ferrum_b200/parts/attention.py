@@ -47,6 +47,7 @@ class PagedAttention(Mixer):
         self.position, self.dtype, self.window = position, dtype, int(window)
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
         self.chunked = False     # True: `window` is a chunk length (a subclass sets it)
+        self.score_softcap, self.sink = 0.0, False      # (a subclass may bend the scores and add a sink to the softmax)
         self.w_q_weight = self.w_k_weight = self.w_v_weight = self.w_output_weight = None
         self.w_qkv = None
         self._tc_tokens = {}     # cache shape -> tokens per tile of the tcgen05 kernel (0: not applicable)
@@ -102,7 +103,8 @@ class PagedAttention(Mixer):
             part = ctx.buf("attn_generic_part", (T * Hq * slots * (D + 2),), torch.float32)
         ops.attention_generic(qkv, out, T, ctx.positions, ctx.req_of_token, table, cache.plane, cache.page_stride,
                               cache.page_size, Hq, Hkv, D, self.scale, self.window, ctx.err, part, slots,
-                              q_start=ctx.q_start, n_reqs=ctx.n_reqs, distance_penalty=distance_penalty, chunked=self.chunked)
+                              q_start=ctx.q_start, n_reqs=ctx.n_reqs, distance_penalty=distance_penalty, chunked=self.chunked,
+                              softcap=self.score_softcap, sink=self.sink)
 
     def plan(self, ctx, cache):
         """The step's work lists of the tensor-core kernels for this layer's shape (None on the

@@ -42,6 +42,12 @@ class ParamSpec:
     init: object = "normal"       # random-weights mode: "normal" N(0, .02), "ones_normal" 1 + N(0, .02), another name
                                   # registered in weights/random_init.py, or a function (shape, generator, device, std)
     optional: bool = False        # may be absent from the file (e.g. a tied output matrix)
+    free: Tuple[int, ...] = ()    # axes whose size the file decides (the part reads it off the tensor in `finalize`);
+                                  # `shape` holds there the size that random weights are drawn with
+
+    def fits(self, shape) -> bool:
+        shape = tuple(shape)
+        return len(shape) == len(self.shape) and all(a == b or i in self.free for i, (a, b) in enumerate(zip(shape, self.shape)))
 
 
 @dataclass(frozen=True)

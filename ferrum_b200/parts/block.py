@@ -32,6 +32,56 @@ class PreNormBlock(Part):
         self.ffn.forward(x, ctx, h)
 
 
+class PostNormBlock(Part):
+    """The norms sit on the sublayers' results and the sublayers read the residual row itself:
+
+        h += ls1 * norm1(mixer(h));   h += ls2 * norm2(ffn(h))
+
+    with norm(v) = v / sqrt(mean(v^2) + eps) * w and ls1, ls2 per-element layer scales (`layer_scale=False`: none).
+    `ffn` (with norm2 and ls2) may be None.  In a 16-bit model the sublayers read the row rounded to the compute type:
+    the step's buffer `residual_copy`, which the embedding fills (`TokenEmbedding(copy_dtype=...)`) and the kernel
+    that adds a sublayer's normed result rewrites.  The sublayers hand their results over in a float32 buffer
+    (`accumulate=False`).  The reference's block is `PreNormBlock`."""
+    graph_safe = True
+
+    def __init__(self, width, dtype, norm1: Norm, mixer: Mixer, norm2: Norm = None, ffn: FeedForward = None, layer_scale=True,
+                 names=("norm1.", "mix.", "norm2.", "mlp.")):
+        if (norm2 is None) != (ffn is None):
+            raise ValueError("the second norm and the feed-forward come together")
+        self.width, self.dtype = width, dtype
+        self.norm1, self.mixer, self.norm2, self.ffn, self.layer_scale = norm1, mixer, norm2, ffn, bool(layer_scale)
+        self._names = names
+        self.w_ls1 = self.w_ls2 = None
+
+    def param_specs(self):
+        if not self.layer_scale:
+            return {}
+        out = {"ls1": ParamSpec((self.width,), kind="vector", init="ones_normal")}
+        if self.ffn is not None:
+            out["ls2"] = ParamSpec((self.width,), kind="vector", init="ones_normal")
+        return out
+
+    def children(self):
+        out = [(self._names[0], self.norm1), (self._names[1], self.mixer)]
+        if self.ffn is not None:
+            out += [(self._names[2], self.norm2), (self._names[3], self.ffn)]
+        return out
+
+    def forward(self, h, ctx, cache):
+        ctx.flush_residual()
+        T, cap, E = ctx.n_tokens, ctx.token_capacity, self.width
+        wide = self.dtype == torch.float32
+        x = h if wide else ctx.buf("residual_copy", (cap, E), self.dtype)
+        y = ctx.buf("post_y", (cap, E), torch.float32)
+        self.mixer.forward(x, ctx, cache, y, accumulate=False)
+        ctx.flush_residual()
+        ops.post_norm_add(h, T, y, self.norm1.w_weight, self.w_ls1, self.norm1.eps, xc=None if wide else x)
+        if self.ffn is not None:
+            self.ffn.forward(x, ctx, y, accumulate=False)
+            ctx.flush_residual()
+            ops.post_norm_add(h, T, y, self.norm2.w_weight, self.w_ls2, self.norm2.eps, xc=None if wide else x)
+
+
 # Up to this many tokens in a step the block's second chain (gates, feed-forward) runs on a second stream.
 OVERLAP_MAX_TOKENS = 64
 

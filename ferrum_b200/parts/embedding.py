@@ -18,13 +18,16 @@ from .linear import STORE_F32, linear
 class TokenEmbedding(Part):
     graph_safe = True
 
-    def __init__(self, n_vocab, width, scale=1.0, positions: "LearnedPositions" = None, copies=1):
+    def __init__(self, n_vocab, width, scale=1.0, positions: "LearnedPositions" = None, copies=1, copy_dtype=None):
         """positions: a `LearnedPositions` part whose vector for a token's position is added to the
         (scaled) embedding; the model lists it as its position encoding, which owns the table.
         copies > 1: the residual rows are [tokens, copies * width], every copy the embedded token (a
-        model whose blocks keep several residual streams)."""
+        model whose blocks keep several residual streams).  copy_dtype (a 16-bit type): the rows are also left
+        in that type in the step's buffer `residual_copy`, for blocks whose sublayers read the residual row
+        itself (`PostNormBlock`, which keeps the copy up to date)."""
         self.n_vocab, self.width, self.scale, self.positions = n_vocab, width, float(scale), positions
         self.copies = int(copies)
+        self.copy_dtype = copy_dtype if copy_dtype not in (None, torch.float32) else None
         self.w_weight = None
 
     def param_specs(self):
@@ -35,6 +38,8 @@ class TokenEmbedding(Part):
         pos = self.positions.w_weight if self.positions is not None else None
         ops.embedding(self.w_weight, ctx.token_ids, h, ctx.err, scale=self.scale, pos_table=pos,
                       positions=ctx.positions if pos is not None else None, copies=self.copies)
+        if self.copy_dtype is not None:
+            ops.post_norm_add(h, ctx.n_tokens, xc=ctx.buf("residual_copy", (ctx.token_capacity, h.shape[1]), self.copy_dtype))
         return h
 
 

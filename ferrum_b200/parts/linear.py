@@ -49,9 +49,12 @@ def linear(x, w, out, mode, ctx, M=None):
         ops.gemm_generic(x, w, out, _GENERIC[mode], M=M)
 
 
-def linear_swiglu(x, w_gate_up, act, F, ctx, M=None, kind="silu"):
+_GLU_EPILOGUE = {"silu": ops.TC_SWIGLU, "gelu_tanh": ops.TC_GEGLU, "swish_clamp": ops.TC_SWISH_CLAMP}
+
+
+def linear_swiglu(x, w_gate_up, act, F, ctx, M=None, kind="silu", limit=0.0):
     """act = silu(x @ w_gate_up[:F].T) * (x @ w_gate_up[F:].T) in one kernel (kind="gelu_tanh": that
-    activation on the gate instead; always the product's own epilogue, never left in partials).  The
+    activation on the gate instead, "swish_clamp": the clamped unit of gate and up with `limit`; always the product's own epilogue, never left in partials).  The
     caller checks `ops.gemm_tc_supported` first."""
     M = x.shape[0] if M is None else M
     if M == 0:
@@ -65,4 +68,4 @@ def linear_swiglu(x, w_gate_up, act, F, ctx, M=None, kind="silu"):
     # (with many tokens the library runs both products as one on its CTA-pair kernel, gate and
     # up rows interleaved, and applies the activation in that kernel's epilogue)
     ws, cnt = ctx.gemm_scratch(M, F, K, True)
-    ops.gemm_tc(x, w_gate_up, act, ops.TC_SWIGLU if kind == "silu" else ops.TC_GEGLU, ctx.err, ws, cnt, M=M, N=F, dual_offset=F)
+    ops.gemm_tc(x, w_gate_up, act, _GLU_EPILOGUE[kind], ctx.err, ws, cnt, M=M, N=F, dual_offset=F, glu_limit=limit)

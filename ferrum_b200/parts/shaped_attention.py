@@ -15,7 +15,13 @@ What a configuration may switch on, each with its constants as parameters:
   dim != vdim    key and value heads of different sizes share pages of max(dim, vdim)-element rows
   qkv_bias       q, k and v projections have bias vectors
   qk_norm        every q and k head is divided by its root mean square and multiplied by a weight
-                 vector shared by all heads, BEFORE the turn
+                 vector shared by all heads, BEFORE the turn; "whole": the root mean square runs over a
+                 token's whole query (key) projection, all heads at once, and the weight vector is as
+                 long as that projection
+  value_from_key no value matrix: the value of a KV head is its key head as projected (before norm and
+                 turn); vdim = dim
+  score_softcap  c > 0: the scaled score becomes c * tanh(score / c)
+  sink           a key of score 0 without a value joins every softmax: weight_j = e^(s_j) / (1 + sum e^s)
   query_temperature  (coef, every): a query at position p is multiplied by
                  1 + coef * ln(floor((p + 1) / every) + 1)
   linear_bias    per-head slopes m[h]: m[h] * (i - j) is taken off the scaled score (numbers, not tensors)
@@ -46,8 +52,16 @@ class ShapedAttention(PagedAttention):
 
     def __init__(self, width, n_head, n_head_kv, dim, vdim, dtype, scale, eps=1e-6, window=0, rotary=None, unit_norm=False,
                  value_rotary=None, distance_penalty=False, gate=False, mask="window", qkv_bias=False, qk_norm=False,
-                 query_temperature=None, linear_bias=None, value_mix=None, value_mix_key="v_first"):
+                 query_temperature=None, linear_bias=None, value_mix=None, value_mix_key="v_first", value_from_key=False,
+                 score_softcap=0.0, sink=False):
         super().__init__(width, n_head, n_head_kv, max(int(dim), int(vdim)), rotary, dtype, window=window, scale=scale)
+        self.score_softcap, self.sink = float(score_softcap or 0.0), bool(sink)
+        self.value_from_key = bool(value_from_key)
+        if self.value_from_key and (int(dim) != int(vdim) or qkv_bias or value_rotary is not None or value_mix is not None):
+            raise ValueError("values taken from the keys have the keys' size, no bias, no turn and no blend")
+        if qk_norm not in (False, True, "head", "whole"):
+            raise ValueError(f"unknown query/key norm {qk_norm!r}")
+        self.whole_norm = qk_norm == "whole"
         self.Dk, self.Dv, self.eps = int(dim), int(vdim), float(eps)
         self.unit_norm, self.value_rotary = bool(unit_norm), value_rotary
         self.has_penalty, self.has_gate = bool(distance_penalty), bool(gate)
@@ -80,6 +94,8 @@ class ShapedAttention(PagedAttention):
         E = self.width
         out = {"q.weight": ParamSpec((self.Hq * self.Dk, E)), "k.weight": ParamSpec((self.Hkv * self.Dk, E)),
                "v.weight": ParamSpec((self.Hkv * self.Dv, E)), "output.weight": ParamSpec((E, self.Hq * self.Dv))}
+        if self.value_from_key:
+            del out["v.weight"]
         if self.has_penalty:
             out["r1"] = ParamSpec((self.Hq,), kind="vector", init="uniform")
             out["r2"] = ParamSpec((self.Hq,), kind="vector", init="uniform")
@@ -89,14 +105,16 @@ class ShapedAttention(PagedAttention):
             out.update({"q.bias": ParamSpec((self.Hq * self.Dk,), kind="vector"), "k.bias": ParamSpec((self.Hkv * self.Dk,), kind="vector"),
                         "v.bias": ParamSpec((self.Hkv * self.Dv,), kind="vector")})
         if self.qk_norm:
-            out.update({"q.norm.weight": ParamSpec((self.Dk,), kind="vector", init="ones_normal"),
-                        "k.norm.weight": ParamSpec((self.Dk,), kind="vector", init="ones_normal")})
+            nq, nk = (self.Hq * self.Dk, self.Hkv * self.Dk) if self.whole_norm else (self.Dk, self.Dk)
+            out.update({"q.norm.weight": ParamSpec((nq,), kind="vector", init="ones_normal"),
+                        "k.norm.weight": ParamSpec((nk,), kind="vector", init="ones_normal")})
         if self.value_mix is not None:
             out["vmix"] = ParamSpec((), kind="vector", init="uniform")      # (read by the blending layers only)
         return out
 
     def finalize(self):
-        rows = [self.w_q_weight, self.w_k_weight, self.w_v_weight] + ([self.w_g_weight] if self.has_gate else [])
+        rows = [self.w_q_weight, self.w_k_weight] + ([] if self.value_from_key else [self.w_v_weight])
+        rows += [self.w_g_weight] if self.has_gate else []
         self.w_in = torch.cat(rows, dim=0).contiguous()
         self.w_q_weight = self.w_k_weight = self.w_v_weight = self.w_g_weight = None
         if self.has_bias:
@@ -129,7 +147,8 @@ class ShapedAttention(PagedAttention):
                       vrot.cos_sin if vrot is not None else None, vrot.pairing if vrot is not None else 0, self.unit_norm,
                       self.eps, q, cache.plane, cache.page_stride, cache.page_size, Hq, Hkv, Dk, Dv, Dp, cache.writes,
                       bias=self.w_bias, q_norm=self.w_q_norm_weight if self.qk_norm else None,
-                      k_norm=self.w_k_norm_weight if self.qk_norm else None, q_temp=self.q_temp, value_mix=mix)
+                      k_norm=self.w_k_norm_weight if self.qk_norm else None, q_temp=self.q_temp, value_mix=mix,
+                      whole_norm=self.whole_norm, value_from_key=self.value_from_key)
         penalty = (self.w_r1, self.w_r2) if self.has_penalty else ((self.slopes, None) if self.slopes is not None else None)
         out = ctx.buf("sattn_out", (cap, Hq * Dv), self.dtype)
         if Dp == Dv and vrot is None and not self.has_gate:
@@ -149,7 +168,7 @@ class ShapedAttention(PagedAttention):
     def _finish(self, o, out, proj, ctx, vrot):
         """Turn back, gate, drop the padding past vdim and round once."""
         T, Hq, Hkv, Dk, Dv, Dp = ctx.n_tokens, self.Hq, self.Hkv, self.Dk, self.Dv, self.D
-        off = Hq * Dk + Hkv * (Dk + Dv)
+        off = Hq * Dk + Hkv * (Dk if self.value_from_key else Dk + Dv)
         gate = proj[:, off:off + Hq * Dv] if self.has_gate else None
         ops.attention_finish(o, T, ctx, vrot.cos_sin if vrot is not None else None, vrot.pairing if vrot is not None else 0,
                              gate, out, Hq, Dv, Dp)

@@ -74,9 +74,10 @@ def check_weights(specs, available, rename=None):
             unexpected.append(fname)
             continue
         found[canon] = fname
-        want = tuple(specs[canon].shape)
-        if tuple(shape) != want:
-            wrong.append(f"{fname}: shape {list(shape)}, expected {list(want)}")
+        spec = specs[canon]
+        if not spec.fits(shape):
+            want = ["any" if i in spec.free else n for i, n in enumerate(spec.shape)]
+            wrong.append(f"{fname}: shape {list(shape)}, expected {want}")
     missing = [n for n, s in specs.items() if n not in found and not s.optional]
     if missing or unexpected or wrong:
         back = {v: k for k, v in rename.items()}

@@ -3,7 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
                     [--model llama31-8b|llama32-3b|llama2-7b] [--dtype bf16|fp16|fp32]
-                    [--workload decode|serve|latent|hybrid|streams] [--layers L] [--batch B] [--context S] [--trials N] [--size 2b|8b]
+                    [--workload decode|serve|latent|hybrid|streams|delta] [--layers L] [--batch B] [--context S] [--trials N] [--size 2b|8b]
 
 Prints ONE JSON line.
 
@@ -41,6 +41,12 @@ feed-forward, chunked rotary attention with biased, normed heads + eight experts
 two, windowed + experts, chunked + dense; values blended with the first layer's; tied output matrix with
 a soft cap) beside a Llama of equal width, heads, KV heads, layers and feed-forward width (the two chosen
 experts together are as wide as the dense feed-forward).
+
+`--workload delta`: the same comparison for the Pererax design (norms on the sublayers' results; layers in turn: a
+pair of causal attention with a soft cap and a sink beside a matrix-memory recurrence, windowed attention whose
+values are its keys, and two gated delta rules with a decay per key channel; every layer with eight clamped experts
+plus two identity outputs, two per token, and a unit for every token) beside the closest of the other designs, a
+Vikupel of equal width, heads, layers and active feed-forward width.
 
 Weights are random N(0, 0.02); token ids are uniform random from a seed.  No L2 flush is needed
 between steps: a step reads gigabytes of weights, far more than the 126 MB L2 holds.
@@ -187,8 +193,8 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (named in config)")
     ap.add_argument("--model", default="llama31-8b", choices=sorted(MODELS), help="layer sizes (random weights)")
     ap.add_argument("--dtype", default="bf16", choices=sorted(DTYPES), help="compute dtype; fp32 is the true 32-bit path")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serve", "latent", "hybrid", "streams"])
-    ap.add_argument("--size", default="2b", choices=sorted(LATENT_SIZES), help="latent, hybrid, streams: the layer sizes to compare at")
+    ap.add_argument("--workload", default="decode", choices=["decode", "serve", "latent", "hybrid", "streams", "delta"])
+    ap.add_argument("--size", default="2b", choices=sorted(LATENT_SIZES), help="latent, hybrid, streams, delta: the layer sizes to compare at")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=None,
                     help="cached tokens per request of the headline point (default 8192 for llama31-8b, 4096 for "
@@ -213,6 +219,8 @@ def main():
         return latent(args, design="vikupel")
     if args.workload == "streams":
         return latent(args, design="zavesun")
+    if args.workload == "delta":
+        return latent(args, design="pererax")
     return decode(args)
 
 
@@ -580,8 +588,40 @@ def stream_configs(size, layers, vocab=32000, window=1024):
     return ours, llama
 
 
-DESIGNS = {"ruperax": ("Ruperax", latent_configs, LATENT_SIZES, 4096), "vikupel": ("Vikupel", hybrid_configs, HYBRID_SIZES, 1024),
-           "zavesun": ("Zavesun", stream_configs, STREAM_SIZES, 1024)}
+# Pererax at the same two widths: attention heads of 128 (a quarter as many KV heads), recurrent heads with a 128 x 128
+# memory each, eight experts a quarter as wide as the dense feed-forward plus two identity outputs, two per token, and
+# a unit for every token half as wide as the dense feed-forward (so a token's active width equals the dense one).
+DELTA_SIZES = {
+    "2b": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, memory_heads=16, rank=128, experts=8, identity=2, top=2,
+               expert_ff=1408, shared_ff=2816),
+    "8b": dict(width=4096, heads=32, kv_heads=8, dim=128, vdim=128, memory_heads=32, rank=128, experts=8, identity=2, top=2,
+               expert_ff=3584, shared_ff=7168),
+}
+
+
+def delta_configs(size, layers, vocab=32000, window=1024):
+    """Layers in turn: the pair (sink attention beside matrix memory), windowed attention with its keys as values,
+    delta rule, delta rule; and the Vikupel of equal size beside it."""
+    s = DELTA_SIZES[size]
+    att = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["vdim"], "scale": s["dim"] ** -0.5,
+           "rot": {"base": 500000.0, "dims": s["dim"]}}
+    memory = {"heads": s["memory_heads"], "dim": s["dim"], "vdim": s["vdim"], "gate_cap": 15.0}
+    delta = {"heads": s["memory_heads"], "kv_heads": s["memory_heads"], "dim": s["dim"], "vdim": s["vdim"], "conv": 4,
+             "decay_rank": s["rank"], "gate_rank": s["rank"]}
+    mlp = {"kind": "moe", "expert": {"ff": s["expert_ff"], "limit": 7.0}, "shared": {"ff": s["shared_ff"], "limit": 7.0},
+           "router": {"experts": s["experts"], "identity": s["identity"], "top": s["top"], "scale": 2.0}}
+    kinds = [{"type": "parallel", "mixer": {"left": dict(att, softcap=30.0), "right": memory}},
+             {"type": "attention", "mixer": dict(att, mask={"size": window})},
+             {"type": "channel_delta", "mixer": delta}, {"type": "channel_delta", "mixer": delta}]
+    ours = {"architecture": "Pererax", "vocab": vocab, "width": s["width"], "norm": {"eps": 1e-6},
+            "layers": [dict(kinds[i % 4], mlp=mlp) for i in range(layers)]}
+    return ours, hybrid_configs(size, layers, vocab, window)[0]
+
+
+# design -> (title, configs of the design and of the model beside it, sizes, window, what stands beside it)
+DESIGNS = {"ruperax": ("Ruperax", latent_configs, LATENT_SIZES, 4096, "llama"), "vikupel": ("Vikupel", hybrid_configs, HYBRID_SIZES, 1024, "llama"),
+           "zavesun": ("Zavesun", stream_configs, STREAM_SIZES, 1024, "llama"),
+           "pererax": ("Pererax", delta_configs, DELTA_SIZES, 1024, "vikupel")}
 
 
 def latent(args, design="ruperax"):
@@ -607,9 +647,9 @@ def latent(args, design="ruperax"):
     gen = torch.Generator().manual_seed(0)
     out = {}
     with ClockSampler() as clk:
-        title, make_configs, all_sizes, window = DESIGNS[design]
+        title, make_configs, all_sizes, window, beside = DESIGNS[design]
         configs = make_configs(args.size, L)
-        for name, cfgd in zip((design, "llama"), configs):
+        for name, cfgd in zip((design, beside), configs):
             arch = registry.lookup(registry.architecture_name(cfgd))
             cfg = arch.read_config(cfgd)
             model = arch.build(cfg, td, "cuda", max_positions=max_len)
@@ -693,7 +733,7 @@ def latent(args, design="ruperax"):
                            vocab=32000, page_size=page,
                            parallelism="single GPU", l2="weights of a step exceed the L2 at these sizes"),
             "clocks": clk.summary(), "gpu_launches": int(ours["decode_launches_per_step"] * K), "peaks": pk,
-            design: ours, "llama_equal_size": out["llama"]}
+            design: ours, beside + "_equal_size": out[beside]}
     print(json.dumps(line))
     return 0
 

@@ -26,12 +26,13 @@ def assert_close_f32(x, ref, what=""):
     assert not bad.any(), f"{what}: {bad.sum()} of {bad.size} differ, worst {np.abs(x - ref).max():.3e} at {np.argwhere(bad)[0]}"
 
 
-def assert_close_16bit(x, ref, what="", dtype="bfloat16"):
-    """Rows of logits [n, V] against the plain implementation's, for a 16-bit compute dtype."""
+def assert_close_16bit(x, ref, what="", dtype="bfloat16", c=None):
+    """Rows of logits [n, V] against the plain implementation's, for a 16-bit compute dtype.  c: another bound than
+    the suite's, for a design whose logits answer to rounding more strongly (its tests say why)."""
     x, ref = np.atleast_2d(np.asarray(x, dtype=np.float64)), np.atleast_2d(np.asarray(ref, dtype=np.float64))
     assert x.shape == ref.shape, (x.shape, ref.shape)
     assert np.isfinite(x).all(), f"{what}: non-finite logits"
-    c = C_16BIT[dtype]
+    c = C_16BIT[dtype] if c is None else c
     spread = ref.std(axis=-1)
     bound = c * spread
     err = np.abs(x - ref).max(axis=-1)

@@ -266,21 +266,29 @@ def clamped_unit(x, w, pre, limit, round_to=None):
     return matmul(g * torch.sigmoid(1.702 * g) * (u + 1.0), w[pre + "down"], round_to)
 
 
-def route(x, w, pre, r, round_to=None):
+def route(x, w, pre, r, round_to=None, margins=None):
     """(chosen [T, top] indices, weights [T, top], scores [T, n]): softmax scores over experts + identity
-    outputs; the choice adds the correction vector, the weights do not and are scaled, not renormalised."""
+    outputs; the choice adds the correction vector, the weights do not and are scaled, not renormalised.
+    `margins` (a list) receives, per token, by how much the last chosen output beats the first one left out,
+    in units of the spread of the token's choice scores (infinite when every output is chosen)."""
     z = matmul(x, w[pre + "router"], round_to)
     s = torch.softmax(z, dim=-1)
     pick = s + w[pre + "correction"]
     # a tie goes to the lower index: stable sort, descending
-    idx = torch.sort(pick, dim=-1, descending=True, stable=True).indices[:, :r["top"]]
-    return idx, torch.gather(s, 1, idx) * r["scale"], s
+    order = torch.sort(pick, dim=-1, descending=True, stable=True)
+    idx = order.indices[:, :r["top"]]
+    if margins is not None:
+        if pick.shape[1] > r["top"]:
+            margins.append((order.values[:, r["top"] - 1] - order.values[:, r["top"]]) / pick.std(dim=-1).clamp_min(1e-30))
+        else:
+            margins.append(torch.full((x.shape[0],), math.inf, dtype=F64))
+    return idx, torch.gather(s, 1, idx) * r.get("scale", 1.0), s
 
 
-def mixture(x, w, pre, mlp, round_to=None):
+def mixture(x, w, pre, mlp, round_to=None, margins=None):
     r = mlp["router"]
     n_real, n_id = r["experts"], r.get("identity", 0)
-    idx, wt, _ = route(x, w, pre, r, round_to)
+    idx, wt, _ = route(x, w, pre, r, round_to, margins)
     y = torch.zeros_like(x)
     xr = rnd(x, round_to)
     for e in range(n_real + n_id):
@@ -313,8 +321,9 @@ def mixer(kind, x, w, pre, m, eps, round_to=None):
     raise ValueError(kind)
 
 
-def forward(cfg, w, tokens, round_to=None, trace=None):
-    """Logits [T, vocab] of one sequence; `trace` (a list) receives x after every layer."""
+def forward(cfg, w, tokens, round_to=None, trace=None, margins=None):
+    """Logits [T, vocab] of one sequence; `trace` (a list) receives x after every layer, `margins` (a list) every
+    router's margins per token (see `route`)."""
     eps = cfg["norm"]["eps"]
     x = w["embed"][torch.tensor(tokens, dtype=torch.long)].clone()
     for i, layer in enumerate(cfg["layers"]):
@@ -322,7 +331,7 @@ def forward(cfg, w, tokens, round_to=None, trace=None):
         y = mixer(layer["type"], x, w, p + "mix.", layer["mixer"], eps, round_to)
         x = x + w[p + "ls1"] * (rms(y, eps) * w[p + "norm1"])
         if layer.get("mlp"):
-            y = mixture(x, w, p + "mlp.", layer["mlp"], round_to)
+            y = mixture(x, w, p + "mlp.", layer["mlp"], round_to, margins)
             x = x + w[p + "ls2"] * (rms(y, eps) * w[p + "norm2"])
         if trace is not None:
             trace.append(x.clone())

@@ -11,14 +11,17 @@
 //                    silu(sum_j w[c][j] * input(t - (taps - 1 - j))[c]) (inputs before the portion's first token come
 //                    from u, all zero before a sequence's first token); a q or k head is then divided by
 //                    sqrt(sum of its squares + 1e-6), and q also multiplied by D^(-1/2).  The last H slots are the
-//                    decays: dec[h][d] = exp(-exp(A_log[h]) * softplus(logit[h D + d] + dt_bias[h D + d])).
+//                    decays: dec[h][d] = exp(-exp(A_log[h]) * softplus(logit[h D + d] + dt_bias[h D + d])), and behind
+//                    them beta[h] = sigmoid(its logit): a token's row of `dec` is [H D | H].
 // delta_conv_state:  u <- the last taps - 1 inputs after this portion; a launch of its own, so that nobody reads u while
 //                    it changes.
-// delta_scan:        a block per (request, head, 32 value columns) walks the portion's tokens in order:
+// delta_scan:        a block per (request, head, a group of value columns) walks the portion's tokens in order:
 //                      S <- dec * S (row d by dec[d]);  e = beta * (v - S^T k);  S <- S + k e^T;  o = S^T q
-//                    with beta = sigmoid(its logit).  Four lanes share a column (rows d = 4 i + quarter each) and add
-//                    their parts by two shuffles: one fixed tree, token by token whatever the portion, so a token's
-//                    result does not depend on how the sequence was cut.
+//                    (o is formed as S^T q of the decayed S plus e (k . q), so that both sums over the rows and k . q
+//                    cross the lanes side by side)
+//                    with beta = sigmoid(its logit).  D / 8 lanes share a column (eight rows each; a lane adds its rows
+//                    into four sums that it folds pairwise) and add their parts by shuffles: one fixed tree, token by
+//                    token whatever the portion, so a token's result does not depend on how the sequence was cut.
 #include "common.cuh"
 
 constexpr int DR_MAX_TAPS = 16;
@@ -38,13 +41,15 @@ delta_prep_kernel(const float* __restrict__ proj, int ldp, const float* __restri
   if (item >= (long long)n_tokens * n_slots) return;
   const int t = (int)(item / n_slots), slot = (int)(item % n_slots);
   const int C = 2 * G * D + H * Dv;
-  if (slot >= 2 * G + H) {                                  // a head's decays
+  if (slot >= 2 * G + H) {                                  // a head's decays, and its beta behind all heads' decays
     const int h = slot - 2 * G - H;
     const float rate = expf(a_log[h]);
+    float* row = dec + (size_t)t * (H * D + H);
     for (int d = lane; d < D; d += 32) {
       const int c = h * D + d;
-      dec[(size_t)t * H * D + c] = expf(-rate * dr_softplus(logit[(size_t)t * ldl + c] + dt_bias[c]));
+      row[c] = expf(-rate * dr_softplus(logit[(size_t)t * ldl + c] + dt_bias[c]));
     }
+    if (lane == 0) row[H * D + h] = 1.f / (1.f + expf(-proj[(size_t)t * ldp + C + h]));
     return;
   }
   const bool is_v = slot >= 2 * G;
@@ -97,66 +102,116 @@ delta_conv_state_kernel(const float* __restrict__ proj, int ldp, int C, int taps
     if (s < taps - 1) u[(size_t)s * C + c] = keep[s];
 }
 
-// RQ rows a thread (D <= 4 RQ), TC tokens staged at a time.  Thread: column tid / 4 of the block's 32, rows 4 i + tid % 4.
-template <int RQ, int TC>
-__global__ void __launch_bounds__(128)
-delta_scan_kernel(const float* __restrict__ qkv, int C, const float* __restrict__ dec, const float* __restrict__ proj, int ldp,
-                  int off_beta, float* __restrict__ state, long long state_stride, const int* __restrict__ q_start,
-                  const int* __restrict__ slots, float* __restrict__ o, int ldo, int H, int G, int D, int Dv) {
-  constexpr int W = 4 * RQ;
-  __shared__ float sq[TC][W], sk[TC][W], sg[TC][W], sv[TC][32], sb[TC];
-  const int tid = threadIdx.x, col = tid >> 2, qd = tid & 3;
-  const int j = blockIdx.x * 32 + col, h = blockIdx.y, r = blockIdx.z;
+__device__ __forceinline__ void dr_cp_async4(float* smem, const float* gmem) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(a), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void dr_cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void dr_cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+// LPC lanes share a value column (D <= 8 LPC): lane q of them holds rows d = LPC i + q, i < 8, of the column in registers,
+// and a block of 256 threads walks 256 / LPC columns.  TC tokens are staged at a time; a staged token row keeps the lanes'
+// elements apart (lane q at 12 q + i, so that a lane reads its rows four at a time and the lanes' 16-byte reads spread over
+// the banks).  The chunk after the one being walked is on its way meanwhile, element by element with cp.async straight to
+// its place (loads into registers that were still pending held up the walk's own shared-memory reads and its stores); a
+// token's operands are read one token ahead of their use.
+template <int LPC, int TC>
+__global__ void __launch_bounds__(256)
+delta_scan_kernel(const float* __restrict__ qkv, int C, const float* __restrict__ dec, float* __restrict__ state,
+                  long long state_stride, const int* __restrict__ q_start, const int* __restrict__ slots, float* __restrict__ o,
+                  int ldo, int H, int G, int D, int Dv) {
+  constexpr int RQ = 8, QS = RQ + 4, W = LPC * QS, WD = LPC * RQ, CB = 256 / LPC;
+  constexpr int LD = (TC * 3 * WD + 255) / 256;
+  static_assert(TC * CB <= 256 && TC <= 256, "one copy a thread brings a chunk's values");
+  __shared__ __align__(16) float sq[2][TC + 1][W], sk[2][TC + 1][W], sg[2][TC + 1][W];      // (one row more: the walk reads a token ahead)
+  __shared__ float sv[2][TC][CB], sb[2][TC], so[2][TC][CB];    // (so: a chunk's read-outs, written out together after its walk)
+  const int tid = threadIdx.x, col = tid / LPC, q = tid % LPC;
+  const int j = blockIdx.x * CB + col, h = blockIdx.y, r = blockIdx.z;
   const int g = h / (H / G);
   const int t0 = q_start[r], t1 = q_start[r + 1];
+  const int ldd = H * D + H;
   float* Sg = state + (long long)slots[r] * state_stride + (size_t)h * D * Dv;
+  const int off_q = g * D, off_k = G * D + g * D, off_v = 2 * G * D + h * Dv + blockIdx.x * CB;
+  auto stage = [&](int c0, int b) {              // a chunk's elements on their way into buffer b
+    const int nt = min(TC, t1 - c0);
+#pragma unroll
+    for (int it = 0; it < LD; ++it) {
+      const int idx = tid + it * 256;
+      const int which = idx / (TC * WD), tk = (idx / WD) % TC, d = idx % WD;
+      if (idx < TC * 3 * WD) {
+        float* dst = (which == 0 ? &sq[b][tk][0] : (which == 1 ? &sk[b][tk][0] : &sg[b][tk][0])) + (d % LPC) * QS + d / LPC;
+        if (tk < nt && d < D) {
+          const size_t row = (size_t)(c0 + tk);
+          dr_cp_async4(dst, which == 0 ? qkv + row * C + off_q + d : (which == 1 ? qkv + row * C + off_k + d : dec + row * ldd + (size_t)h * D + d));
+        } else {
+          *dst = which == 2 ? 1.f : 0.f;
+        }
+      }
+    }
+    if (tid < TC * CB) {
+      const int tk = tid / CB, c = tid % CB;
+      if (tk < nt && blockIdx.x * CB + c < Dv) dr_cp_async4(&sv[b][tk][c], qkv + (size_t)(c0 + tk) * C + off_v + c);
+      else sv[b][tk][c] = 0.f;
+    }
+    if (tid < nt) dr_cp_async4(&sb[b][tid], dec + (size_t)(c0 + tid) * ldd + H * D + h);
+    dr_cp_async_commit();
+  };
+  if (t0 < t1) stage(t0, 0);
   float S[RQ];
 #pragma unroll
   for (int i = 0; i < RQ; ++i) {
-    const int d = 4 * i + qd;
+    const int d = LPC * i + q;
     S[i] = (d < D && j < Dv) ? Sg[(size_t)d * Dv + j] : 0.f;
   }
-  const int off_q = g * D, off_k = G * D + g * D, off_v = 2 * G * D + h * Dv + blockIdx.x * 32;
-  for (int c0 = t0; c0 < t1; c0 += TC) {
+  dr_cp_async_wait_all();
+  __syncthreads();
+  int b = 0;
+  for (int c0 = t0; c0 < t1; c0 += TC, b ^= 1) {
     const int nt = min(TC, t1 - c0);
-    __syncthreads();                                       // the chunk before has been walked
-    for (int idx = tid; idx < nt * W; idx += 128) {
-      const int tk = idx / W, d = idx % W;
-      const size_t row = (size_t)(c0 + tk);
-      sq[tk][d] = d < D ? qkv[row * C + off_q + d] : 0.f;
-      sk[tk][d] = d < D ? qkv[row * C + off_k + d] : 0.f;
-      sg[tk][d] = d < D ? dec[row * H * D + (size_t)h * D + d] : 1.f;
-    }
-    for (int idx = tid; idx < nt * 32; idx += 128) {
-      const int tk = idx >> 5, c = idx & 31;
-      sv[tk][c] = blockIdx.x * 32 + c < Dv ? qkv[(size_t)(c0 + tk) * C + off_v + c] : 0.f;
-    }
-    if (tid < nt) sb[tid] = 1.f / (1.f + expf(-proj[(size_t)(c0 + tid) * ldp + off_beta + h]));
-    __syncthreads();
+    if (c0 + TC < t1) stage(c0 + TC, b ^ 1);     // (that buffer was last read before the barrier that ended the chunk before)
+    const float4* g4 = reinterpret_cast<const float4*>(&sg[b][0][q * QS]);
+    const float4* k4 = reinterpret_cast<const float4*>(&sk[b][0][q * QS]);
+    const float4* q4 = reinterpret_cast<const float4*>(&sq[b][0][q * QS]);
+    float4 ga = g4[0], gb = g4[1], ka = k4[0], kb = k4[1], qa = q4[0], qb = q4[1];
+    float beta = sb[b][0], vj = sv[b][0][col];
     for (int tk = 0; tk < nt; ++tk) {
-      float part = 0.f;
+      // the next token's operands (past the chunk's last token: the spare row, never used)
+      const int nx = (tk + 1) * (W / 4);
+      const float4 ga2 = g4[nx], gb2 = g4[nx + 1], ka2 = k4[nx], kb2 = k4[nx + 1], qa2 = q4[nx], qb2 = q4[nx + 1];
+      const float beta2 = sb[b][min(tk + 1, TC - 1)], vj2 = sv[b][min(tk + 1, TC - 1)][col];
+      // The read-out sees the token's write: (S + k e^T)^T q = S^T q + e (k . q).  So S^T k, S^T q (both of the decayed S)
+      // and k . q are summed across the lanes side by side, and one chain of shuffles serves the token.
+      float kq = (fmaf(kb.x, qb.x, ka.x * qa.x) + fmaf(kb.y, qb.y, ka.y * qa.y)) + (fmaf(kb.z, qb.z, ka.z * qa.z) + fmaf(kb.w, qb.w, ka.w * qa.w));
+      S[0] *= ga.x; S[1] *= ga.y; S[2] *= ga.z; S[3] *= ga.w;
+      S[4] *= gb.x; S[5] *= gb.y; S[6] *= gb.z; S[7] *= gb.w;
+      float part = (fmaf(S[4], kb.x, S[0] * ka.x) + fmaf(S[5], kb.y, S[1] * ka.y)) + (fmaf(S[6], kb.z, S[2] * ka.z) + fmaf(S[7], kb.w, S[3] * ka.w));
+      float po = (fmaf(S[4], qb.x, S[0] * qa.x) + fmaf(S[5], qb.y, S[1] * qa.y)) + (fmaf(S[6], qb.z, S[2] * qa.z) + fmaf(S[7], qb.w, S[3] * qa.w));
 #pragma unroll
-      for (int i = 0; i < RQ; ++i) {
-        S[i] *= sg[tk][4 * i + qd];
-        part = fmaf(S[i], sk[tk][4 * i + qd], part);
+      for (int off = 1; off < LPC; off <<= 1) {
+        const float o1 = __shfl_xor_sync(0xffffffffu, part, off), o2 = __shfl_xor_sync(0xffffffffu, po, off);
+        const float o3 = __shfl_xor_sync(0xffffffffu, kq, off);
+        part += o1;
+        po += o2;
+        kq += o3;
       }
-      part += __shfl_xor_sync(0xffffffffu, part, 1);
-      part += __shfl_xor_sync(0xffffffffu, part, 2);
-      const float e = sb[tk] * (sv[tk][col] - part);
-      float po = 0.f;
-#pragma unroll
-      for (int i = 0; i < RQ; ++i) {
-        S[i] = fmaf(sk[tk][4 * i + qd], e, S[i]);
-        po = fmaf(S[i], sq[tk][4 * i + qd], po);
-      }
-      po += __shfl_xor_sync(0xffffffffu, po, 1);
-      po += __shfl_xor_sync(0xffffffffu, po, 2);
-      if (qd == 0 && j < Dv) o[(size_t)(c0 + tk) * ldo + (size_t)h * Dv + j] = po;
+      const float e = beta * (vj - part);
+      po = fmaf(e, kq, po);
+      S[0] = fmaf(ka.x, e, S[0]); S[1] = fmaf(ka.y, e, S[1]); S[2] = fmaf(ka.z, e, S[2]); S[3] = fmaf(ka.w, e, S[3]);
+      S[4] = fmaf(kb.x, e, S[4]); S[5] = fmaf(kb.y, e, S[5]); S[6] = fmaf(kb.z, e, S[6]); S[7] = fmaf(kb.w, e, S[7]);
+      if (q == 0) so[b][tk][col] = po;
+      ga = ga2; gb = gb2; ka = ka2; kb = kb2; qa = qa2; qb = qb2;
+      beta = beta2; vj = vj2;
+    }
+    dr_cp_async_wait_all();
+    __syncthreads();
+    if (tid < nt * CB) {                         // (the next chunk's walk fills the other buffer; a barrier lies before this one is written again)
+      const int tk = tid / CB, c = tid % CB;
+      if (blockIdx.x * CB + c < Dv) o[(size_t)(c0 + tk) * ldo + (size_t)h * Dv + blockIdx.x * CB + c] = so[b][tk][c];
     }
   }
 #pragma unroll
   for (int i = 0; i < RQ; ++i) {
-    const int d = 4 * i + qd;
+    const int d = LPC * i + q;
     if (d < D && j < Dv) Sg[(size_t)d * Dv + j] = S[i];
   }
 }
@@ -165,7 +220,7 @@ constexpr int DR_MAX_D = 256;
 
 // proj: float32 rows [q | k | v | beta logits] of stride ldp; logit: float32 rows [H * D] of stride ldl (the decays' logits);
 // conv_w: [C][taps]; state: [slots][state_stride] float32 rows, S first and the convolution's inputs from H * D * Dv on;
-// qkv [T][C] and dec [T][H * D]: float32 scratch; o: float32 [T][ldo] receives the heads' read-outs [H * Dv].
+// qkv [T][C] and dec [T][H * D + H]: float32 scratch; o: float32 [T][ldo] receives the heads' read-outs [H * Dv].
 FERRUM_API int ferrum_delta_rule(const float* proj, int ldp, const float* logit, int ldl, int n_tokens, int n_reqs,
                                  const int* req_of_token, const int* q_start, const int* slots, const float* conv_w, int taps,
                                  const float* dt_bias, const float* a_log, int H, int G, int D, int Dv, float* state,
@@ -191,13 +246,13 @@ FERRUM_API int ferrum_delta_rule(const float* proj, int ldp, const float* logit,
                                                                              slots, n_reqs);
     FERRUM_CHECK_LAUNCH("delta_conv_state");
   }
-  const dim3 grid((Dv + 31) / 32, H, n_reqs);
-#define DR_LAUNCH(RQ, TC)                                                                                                      \
-  delta_scan_kernel<RQ, TC><<<grid, 128, 0, stream>>>(qkv, C, dec, proj, ldp, C, state, state_stride, q_start, slots, o, ldo, H, G, D, Dv)
-  if (D <= 32) DR_LAUNCH(8, 16);
-  else if (D <= 64) DR_LAUNCH(16, 16);
-  else if (D <= 128) DR_LAUNCH(32, 16);
-  else DR_LAUNCH(64, 8);
+#define DR_LAUNCH(LPC, TC)                                                                                                     \
+  delta_scan_kernel<LPC, TC><<<dim3((Dv + 256 / LPC - 1) / (256 / LPC), H, n_reqs), 256, 0, stream>>>(                        \
+      qkv, C, dec, state, state_stride, q_start, slots, o, ldo, H, G, D, Dv)
+  if (D <= 32) DR_LAUNCH(4, 4);
+  else if (D <= 64) DR_LAUNCH(8, 8);
+  else if (D <= 128) DR_LAUNCH(16, 8);
+  else DR_LAUNCH(32, 4);
 #undef DR_LAUNCH
   FERRUM_CHECK_LAUNCH("delta_scan");
   return 0;

@@ -41,6 +41,7 @@ def lib():
                     raise KernelError(f"cannot load the kernel library {path}: {e}") from None
                 handle.ferrum_last_error.restype = ctypes.c_char_p
                 handle.ferrum_gemm_tc_workspace.restype = c_longlong
+                handle.ferrum_matrix_memory_state_floats.restype = c_longlong
                 if handle.ferrum_kernels_abi() != ABI:
                     raise KernelError(f"{path} is a stale build; delete it and call again")
                 if os.environ.get("FERRUM_DEPENDENT_LAUNCH", "1") == "0":
@@ -1120,7 +1121,7 @@ def delta_rule(proj, logit, n_tokens, ctx, conv_w, dt_bias, a_log, H, G, D, Dv, 
     """Everything of the gated delta rule between its products: short convolution + silu over q, k, v (its last
     inputs kept in the request's state row), unit norm of q and k, the decays, the walk over the tokens.
     proj: float32 rows [q: G D | k: G D | v: H Dv | beta logits: H]; logit: float32 rows [H D] (decay logits before
-    dt_bias); state: float32 [max_requests, H D Dv + (taps - 1) C]; qkv [T, C], dec [T, H D]: float32 scratch;
+    dt_bias); state: float32 [max_requests, H D Dv + (taps - 1) C]; qkv [T, C], dec [T, H D + H]: float32 scratch;
     o: float32 [T, H Dv]."""
     global launches
     _need(proj, torch.float32, "proj", 2); _need(logit, torch.float32, "logit", 2); _need(state, torch.float32, "state", 2)
@@ -1130,7 +1131,7 @@ def delta_rule(proj, logit, n_tokens, ctx, conv_w, dt_bias, a_log, H, G, D, Dv, 
     for t, n in ((conv_w, "conv_w"), (dt_bias, "dt_bias"), (a_log, "a_log")):
         _need(t, torch.float32, n)
     if (conv_w.shape[0] != C or not conv_w.is_contiguous() or dt_bias.numel() != H * D or a_log.numel() != H
-            or state.shape[1] != H * D * Dv + (taps - 1) * C or qkv.numel() < n_tokens * C or dec.numel() < n_tokens * H * D):
+            or state.shape[1] != H * D * Dv + (taps - 1) * C or qkv.numel() < n_tokens * C or dec.numel() < n_tokens * (H * D + H)):
         raise KernelError("delta_rule: shapes do not agree")
     if _profile is not None:
         global _work
@@ -1144,15 +1145,22 @@ def delta_rule(proj, logit, n_tokens, ctx, conv_w, dt_bias, a_log, H, G, D, Dv, 
 
 
 def matrix_memory_state_size(H, D, Dv):
-    """Floats of a request's state row: S [H, D, Dv] and, per block of 32 value columns, a copy of n [H, D] and m [H]."""
-    return H * D * Dv + ((Dv + 31) // 32) * (H * D + H)
+    """Floats of a request's state row: S [H, D, Dv] and, per eight value columns, a copy of n [H, D] and m [H] (the
+    kernel's own layout: it is asked when the library is there, so that a cache layout can also be made without it)."""
+    if _lib is not None:
+        return int(_lib.ferrum_matrix_memory_state_floats(c_int(H), c_int(D), c_int(Dv)))
+    return H * D * Dv + ((Dv + 7) // 8) * (H * D + H)
 
 
-def matrix_memory(proj, offsets, bias_i, bias_f, cap, n_tokens, ctx, H, D, Dv, state, o):
+def matrix_memory(proj, offsets, bias_i, bias_f, cap, n_tokens, ctx, H, D, Dv, state, gates, o):
     """The walk of the matrix-memory recurrence (see csrc/kernels/matrix_memory.cu).  proj: float32 rows holding q, k,
     v and the two gates' logits at `offsets` = (q, k, v, i, f); state: float32 [max_requests, matrix_memory_state_size];
-    o: float32 [T, H Dv]."""
+    gates: float32 scratch of T * 2 H elements; o: float32 [T, H Dv]."""
+    global launches
     _need(proj, torch.float32, "proj", 2); _need(state, torch.float32, "state", 2); _need(o, torch.float32, "o", 2)
+    _need(gates, torch.float32, "gates")
+    if gates.numel() < n_tokens * 2 * H:
+        raise KernelError("matrix_memory: the gates' scratch is too small")
     _need(bias_i, torch.float32, "bias_i", 1); _need(bias_f, torch.float32, "bias_f", 1)
     oq, ok, ov, oi, of = (int(v) for v in offsets)
     if (bias_i.shape[0] != H or bias_f.shape[0] != H or state.shape[1] != matrix_memory_state_size(H, D, Dv)
@@ -1164,4 +1172,5 @@ def matrix_memory(proj, offsets, bias_i, bias_f, cap, n_tokens, ctx, H, D, Dv, s
     _check(lib().ferrum_matrix_memory(_ptr(proj), c_int(proj.stride(0)), c_int(oq), c_int(ok), c_int(ov), c_int(oi), c_int(of),
                                       _ptr(bias_i), _ptr(bias_f), c_float(cap), c_int(n_tokens), c_int(ctx.n_reqs), _ptr(ctx.q_start),
                                       _ptr(ctx.slots), c_int(H), c_int(D), c_int(Dv), _ptr(state), c_longlong(state.stride(0)),
-                                      _ptr(o), c_int(o.stride(0)), _stream()), "matrix_memory")
+                                      _ptr(gates), _ptr(o), c_int(o.stride(0)), _stream()), "matrix_memory")
+    launches += 1          # (the entry point launches the gates and the walk)

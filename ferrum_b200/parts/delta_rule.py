@@ -107,7 +107,7 @@ class ChannelDeltaMixer(Mixer):
         gate = ctx.buf("delta_gate_logit", (cap, H * Dv), torch.float32)
         linear(low[:, self.ra:], self.w_g2_weight, gate, STORE_F32, ctx, M=T)
         qkv = ctx.buf("delta_qkv", (cap, self.channels), torch.float32)
-        dec = ctx.buf("delta_dec", (cap, H * D), torch.float32)
+        dec = ctx.buf("delta_dec", (cap, H * D + H), torch.float32)
         o = ctx.buf("delta_o", (cap, H * Dv), torch.float32)
         ops.delta_rule(proj, logit, T, ctx, self.w_conv, self.w_dt_bias, self.w_A_log, H, self.G, D, Dv, cache.state, qkv, dec, o)
         out = ctx.buf("delta_out", (cap, H * Dv), self.dtype)

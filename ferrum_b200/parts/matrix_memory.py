@@ -65,7 +65,8 @@ class MatrixMemoryMixer(Mixer):
         oq, ok, ov, og = 0, H * D, 2 * H * D, 2 * H * D + H * Dv
         oi = og + H * Dv
         o = ctx.buf("mmem_o", (cap, H * Dv), torch.float32)
-        ops.matrix_memory(proj, (oq, ok, ov, oi, oi + H), self.w_i_bias, self.w_f_bias, self.cap, T, ctx, H, D, Dv, cache.state, o)
+        gates = ctx.buf("mmem_gates", (cap, 2 * H), torch.float32)
+        ops.matrix_memory(proj, (oq, ok, ov, oi, oi + H), self.w_i_bias, self.w_f_bias, self.cap, T, ctx, H, D, Dv, cache.state, gates, o)
         out = ctx.buf("mmem_out", (cap, H * Dv), self.dtype)
         ops.head_gate_norm(o, proj[:, og:og + H * Dv], self.w_norm_weight, self.eps, T, H, Dv, out)
         if defer and not accumulate:

@@ -38,7 +38,7 @@ sys.path.insert(0, ROOT)
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("kernel", choices=["attn_decode", "attn_prefill", "latent_decode", "latent_prefill", "head_linear", "gemm", "moe", "streams", "rmsnorm",
-                                       "rope", "ssm", "step", "timeline"])
+                                       "rope", "ssm", "delta", "memory", "step", "timeline"])
     ap.add_argument("--kv-rank", type=int, default=512, help="latent_*: elements of the cached latent (the values)")
     ap.add_argument("--rot-dim", type=int, default=64, help="latent_*: rotated key elements behind the latent")
     ap.add_argument("--window", type=int, default=0, help="latent_*: keys a query looks back over (0: all)")
@@ -149,6 +149,31 @@ def main():
                                              xbc, y, out) for st in states]
         work = {"bytes": T * 4 * (inner + 2 * C + H + 3 * inner) + T * inner * esize + 2 * R * inner * N * 4,
                 "flops": 6.0 * T * inner * N, "bound": "ffma"}
+    elif args.kernel in ("delta", "memory"):
+        # --batch requests of --tokens tokens each; --hq heads with keys and values of --head-dim elements:
+        # delta: convolution, unit norm, decays and the walk of the gated delta rule; memory: the walk of the matrix memory
+        H, Dk, R, n = Hq, D, args.batch, args.tokens
+        T = R * n
+        ctx = StepContext(dev, max(16, T), R, [])
+        ctx.fill([StepEntry(r, 0, [1] * n) for r in range(R)], [])
+        f = lambda *shape: torch.randn(*shape, device=dev, generator=gen) * 0.2
+        o = torch.empty(T, H * Dk, device=dev)
+        if args.kernel == "delta":
+            C = 3 * H * Dk
+            proj, logit = f(T, C + H), f(T, H * Dk)
+            conv_w, dt_bias, a_log = f(C, 4), f(H * Dk), f(H)
+            states = [torch.zeros(R, H * Dk * Dk + 3 * C, device=dev) for _ in range(args.layers)]
+            qkv, dec = torch.empty(T, C, device=dev), torch.empty(T, H * Dk + H, device=dev)
+            runs = [lambda st=st: ops.delta_rule(proj, logit, T, ctx, conv_w, dt_bias, a_log, H, H, Dk, Dk, st, qkv, dec, o) for st in states]
+            work = {"bytes": 4 * (T * (2 * C + H + 3 * H * Dk) + 2 * R * H * Dk * Dk), "flops": 6.0 * T * H * Dk * Dk, "bound": "ffma"}
+        else:
+            proj = f(T, 3 * H * Dk + 2 * H)
+            bi, bf = f(H), f(H) + 3.0
+            states = [torch.zeros(R, ops.matrix_memory_state_size(H, Dk, Dk), device=dev) for _ in range(args.layers)]
+            offs = (0, H * Dk, 2 * H * Dk, 3 * H * Dk, 3 * H * Dk + H)
+            gates = torch.empty(T, 2 * H, device=dev)
+            runs = [lambda st=st: ops.matrix_memory(proj, offs, bi, bf, 12.0, T, ctx, H, Dk, Dk, st, gates, o) for st in states]
+            work = {"bytes": 4 * (T * (4 * H * Dk + 2 * H) + 2 * R * H * Dk * Dk), "flops": 4.0 * T * H * Dk * Dk, "bound": "ffma"}
     elif args.kernel in ("latent_decode", "latent_prefill"):
         # attention over cached rows of kv_rank + rot_dim elements, --hq heads sharing them
         decode = args.kernel == "latent_decode"

@@ -270,7 +270,7 @@ def route(x, w, pre, r, round_to=None, margins=None):
     """(chosen [T, top] indices, weights [T, top], scores [T, n]): softmax scores over experts + identity
     outputs; the choice adds the correction vector, the weights do not and are scaled, not renormalised.
     `margins` (a list) receives, per token, by how much the last chosen output beats the first one left out,
-    in units of the spread of the token's choice scores (infinite when every output is chosen)."""
+    in units of the spread of the token's scores (infinite when every output is chosen)."""
     z = matmul(x, w[pre + "router"], round_to)
     s = torch.softmax(z, dim=-1)
     pick = s + w[pre + "correction"]
@@ -279,7 +279,7 @@ def route(x, w, pre, r, round_to=None, margins=None):
     idx = order.indices[:, :r["top"]]
     if margins is not None:
         if pick.shape[1] > r["top"]:
-            margins.append((order.values[:, r["top"] - 1] - order.values[:, r["top"]]) / pick.std(dim=-1).clamp_min(1e-30))
+            margins.append((order.values[:, r["top"] - 1] - order.values[:, r["top"]]) / s.std(dim=-1).clamp_min(1e-30))
         else:
             margins.append(torch.full((x.shape[0],), math.inf, dtype=F64))
     return idx, torch.gather(s, 1, idx) * r.get("scale", 1.0), s

@@ -89,7 +89,8 @@ def test_registry_names_runs_and_cache_layout():
     assert lay.group_planes == [2, 1]                            # both runs of the pair keep pages of their own
     assert lay.run_state == [0, None, 1, 2, 3]                   # ... and every recurrent run a state row of its own
     delta_state = 4 * 10 * 6 + 2 * (2 * 2 * 10 + 4 * 6)
-    assert lay.state_needs[1].shape == (delta_state,) and lay.state_needs[0].shape == (3 * 6 * 10 + 3 * 6 + 3,)
+    assert lay.state_needs[1].shape == (delta_state,)
+    assert lay.state_needs[0].shape == (3 * 6 * 10 + 2 * (3 * 6 + 3),)      # S, and a copy of n and m per eight value columns
 
 
 def test_low_rank_sizes_come_from_the_file_and_wrong_weights_are_listed(tmp_path):

@@ -10,10 +10,10 @@
 //   m' = max(f + m, i);   S <- e^(f + m - m') S + e^(i - m') k v^T;   n <- e^(f + m - m') n + e^(i - m') k
 //   o = S^T q' / (max(|n . q'|, e^(-m')) + 1e-6)          with q' = q D^(-1/2)
 //
-// A block per (request, head, a group of value columns) walks the portion's tokens in order.  D / 8 lanes share a column
-// (eight rows each, and the same rows of n) and add their parts by shuffles: one fixed tree, token by token whatever the
-// portion, so a token's result does not depend on how the sequence was cut.  Every block of a head works out n and m
-// alike and keeps copies of its own in the state (a block may start after another block of its head has finished).
+// A block per (request, head, 32 value columns) walks the portion's tokens in order, token by token whatever the portion,
+// and the sums over the rows have one fixed tree, so a token's result does not depend on how the sequence was cut.  Every
+// block of a head works out n and m alike and keeps copies of its own in the state (a block may start after another block
+// of its head has finished).
 #include "common.cuh"
 
 constexpr int MM_COPY_COLS = 8;      // value columns per copy of n and m in the state row
@@ -39,26 +39,28 @@ matrix_memory_gates_kernel(const float* __restrict__ proj, int ldp, int off_i, i
   gates[(size_t)t * 2 * H + H + h] = mm_logsigmoid(cap * tanhf((row[off_f + h] + bias_f[h]) / cap));
 }
 
-// LPC lanes share a value column (D <= 8 LPC): lane q of them holds rows d = LPC i + q, i < 8, of the column and of n in
-// registers, and a block of 256 threads walks 256 / LPC columns.  TC tokens are staged at a time; a staged token row keeps
-// the lanes' elements apart (lane q at 12 q + i: a lane reads its rows four at a time, the lanes' 16-byte reads spread over
-// the banks).  The chunk after the one being walked is on its way meanwhile, element by element with cp.async straight to
-// its place; a token's operands are read one token ahead of their use.  A block reads the copy of n and m that belongs to
-// its first eight columns and writes the copies of all its columns, so whichever block shape walks the next portion finds
-// every copy up to date.
-template <int LPC, int TC>
-__global__ void __launch_bounds__(256)
+// A block of 128 threads walks 32 value columns: thread (rg, cq) holds rows d = rg RQ .. rg RQ + RQ - 1 (sixteen row groups,
+// D <= 16 RQ) of the four columns 4 cq .. 4 cq + 3, and the same rows of n, in registers.  The memory's update needs no sum
+// across rows, so nothing crosses lanes or warps inside the walk: a token's k and q are broadcast reads of shared memory,
+// and every value read serves four columns (what bounds such a walk is the path from shared memory to the registers: a
+// 16-byte read a lane takes four cycles of it per warp, whatever is broadcast).  Each thread leaves its part of S^T q (and
+// of n . q) in shared memory; after a chunk the block adds the sixteen parts in row order (one fixed tree) and writes the
+// read-outs.  TC tokens are staged at a time, the next chunk on its way meanwhile (cp.async).  A block reads the copy of n
+// and m that belongs to its first eight columns and writes the copies of all its columns.
+constexpr int MM_THREADS = 128, MM_RG = 16, MM_CB = 32;
+
+template <int RQ, int TC>
+__global__ void __launch_bounds__(MM_THREADS)
 matrix_memory_scan_kernel(const float* __restrict__ proj, int ldp, int off_q, int off_k, int off_v, const float* __restrict__ gates,
                           float* __restrict__ state, long long state_stride, const int* __restrict__ q_start,
                           const int* __restrict__ slots, float* __restrict__ o, int ldo, int H, int D, int Dv) {
-  constexpr int RQ = 8, QS = RQ + 4, W = LPC * QS, WD = LPC * RQ, CB = 256 / LPC;
-  constexpr int LD = (TC * 2 * WD + 255) / 256;
-  static_assert(TC * CB <= 256 && CB % MM_COPY_COLS == 0, "one copy a thread brings a chunk's values");
-  __shared__ __align__(16) float sq[2][TC + 1][W], sk[2][TC + 1][W];          // (one row more: the walk reads a token ahead)
-  __shared__ float sv[2][TC][CB], si[2][TC], sf[2][TC];
-  __shared__ float so[2][TC][CB], sn[2][TC][CB], sm[2][TC];         // a chunk's sums and maxima: its read-outs are formed and written after its walk
-  const int tid = threadIdx.x, col = tid / LPC, q = tid % LPC;
-  const int j = blockIdx.x * CB + col, h = blockIdx.y, r = blockIdx.z;
+  constexpr int DP = MM_RG * RQ, NT = MM_THREADS, CB = MM_CB;
+  constexpr int LD = (TC * 2 * DP + NT - 1) / NT, LV = (TC * CB + NT - 1) / NT;
+  static_assert(RQ % 4 == 0 && TC <= NT, "rows are read four at a time");
+  __shared__ __align__(16) float sq[2][TC][DP], sk[2][TC][DP], sv[2][TC][CB], pn[MM_RG][TC][CB];
+  __shared__ float si[2][TC], sf[2][TC], pq[MM_RG][TC], sm[TC];      // pn, pq, sm: the threads' parts of a chunk's sums, and its maxima
+  const int tid = threadIdx.x, cq = tid % (CB / 4), rg = tid / (CB / 4);
+  const int j0 = blockIdx.x * CB + 4 * cq, h = blockIdx.y, r = blockIdx.z;
   const int t0 = q_start[r], t1 = q_start[r + 1];
   float* const base = state + (long long)slots[r] * state_stride;
   float* const Sg = base + (size_t)h * D * Dv;
@@ -70,18 +72,22 @@ matrix_memory_scan_kernel(const float* __restrict__ proj, int ldp, int off_q, in
     const int nt = min(TC, t1 - c0);
 #pragma unroll
     for (int it = 0; it < LD; ++it) {
-      const int idx = tid + it * 256;
-      const int which = idx / (TC * WD), tk = (idx / WD) % TC, d = idx % WD;
-      if (idx < TC * 2 * WD) {
-        float* dst = (which == 0 ? &sq[b][tk][0] : &sk[b][tk][0]) + (d % LPC) * QS + d / LPC;
+      const int idx = tid + it * NT;
+      const int which = idx / (TC * DP), tk = (idx / DP) % TC, d = idx % DP;
+      if (idx < TC * 2 * DP) {
+        float* dst = which == 0 ? &sq[b][tk][d] : &sk[b][tk][d];
         if (tk < nt && d < D) mm_cp_async4(dst, proj + (size_t)(c0 + tk) * ldp + (which == 0 ? off_q : off_k) + h * D + d);
         else *dst = 0.f;
       }
     }
-    if (tid < TC * CB) {
-      const int tk = tid / CB, c = tid % CB;
-      if (tk < nt && blockIdx.x * CB + c < Dv) mm_cp_async4(&sv[b][tk][c], proj + (size_t)(c0 + tk) * ldp + off_v + h * Dv + blockIdx.x * CB + c);
-      else sv[b][tk][c] = 0.f;
+#pragma unroll
+    for (int it = 0; it < LV; ++it) {
+      const int idx = tid + it * NT;
+      const int tk = idx / CB, c = idx % CB;
+      if (idx < TC * CB) {
+        if (tk < nt && blockIdx.x * CB + c < Dv) mm_cp_async4(&sv[b][tk][c], proj + (size_t)(c0 + tk) * ldp + off_v + h * Dv + blockIdx.x * CB + c);
+        else sv[b][tk][c] = 0.f;
+      }
     }
     if (tid < nt) {
       mm_cp_async4(&si[b][tid], gates + (size_t)(c0 + tid) * 2 * H + h);
@@ -90,11 +96,12 @@ matrix_memory_scan_kernel(const float* __restrict__ proj, int ldp, int off_q, in
     mm_cp_async_commit();
   };
   if (t0 < t1) stage(t0, 0);
-  float S[RQ], n[RQ];
+  float S[4][RQ], n[RQ];
 #pragma unroll
   for (int i = 0; i < RQ; ++i) {
-    const int d = LPC * i + q;
-    S[i] = (d < D && j < Dv) ? Sg[(size_t)d * Dv + j] : 0.f;
+    const int d = rg * RQ + i;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) S[c][i] = (d < D && j0 + c < Dv) ? Sg[(size_t)d * Dv + j0 + c] : 0.f;
     n[i] = d < D ? ng[(size_t)x0 * D + d] : 0.f;
   }
   float m = mg[x0];
@@ -104,58 +111,69 @@ matrix_memory_scan_kernel(const float* __restrict__ proj, int ldp, int off_q, in
   int b = 0;
   for (int c0 = t0; c0 < t1; c0 += TC, b ^= 1) {
     const int nt = min(TC, t1 - c0);
-    if (c0 + TC < t1) stage(c0 + TC, b ^ 1);     // (that buffer was last read before the barrier that ended the chunk before)
-    const float4* k4 = reinterpret_cast<const float4*>(&sk[b][0][q * QS]);
-    const float4* q4 = reinterpret_cast<const float4*>(&sq[b][0][q * QS]);
-    float4 ka = k4[0], kb = k4[1], qa = q4[0], qb = q4[1];
-    float ig = si[b][0], fg = sf[b][0], vj = sv[b][0][col];
+    if (c0 + TC < t1) stage(c0 + TC, b ^ 1);     // (that buffer was last read before the barriers that ended the chunk before)
     for (int tk = 0; tk < nt; ++tk) {
-      // the next token's operands (past the chunk's last token: the spare row, never used)
-      const int nx = (tk + 1) * (W / 4), tn = min(tk + 1, TC - 1);
-      const float4 ka2 = k4[nx], kb2 = k4[nx + 1], qa2 = q4[nx], qb2 = q4[nx + 1];
-      const float ig2 = si[b][tn], fg2 = sf[b][tn], vj2 = sv[b][tn][col];
-      const float fm = fg + m;
-      const float m_new = fmaxf(fm, ig);
-      const float a = expf(fm - m_new), bb = expf(ig - m_new);
-      const float bv = bb * vj;
-      S[0] = fmaf(ka.x, bv, a * S[0]); S[1] = fmaf(ka.y, bv, a * S[1]); S[2] = fmaf(ka.z, bv, a * S[2]); S[3] = fmaf(ka.w, bv, a * S[3]);
-      S[4] = fmaf(kb.x, bv, a * S[4]); S[5] = fmaf(kb.y, bv, a * S[5]); S[6] = fmaf(kb.z, bv, a * S[6]); S[7] = fmaf(kb.w, bv, a * S[7]);
-      n[0] = fmaf(ka.x, bb, a * n[0]); n[1] = fmaf(ka.y, bb, a * n[1]); n[2] = fmaf(ka.z, bb, a * n[2]); n[3] = fmaf(ka.w, bb, a * n[3]);
-      n[4] = fmaf(kb.x, bb, a * n[4]); n[5] = fmaf(kb.y, bb, a * n[5]); n[6] = fmaf(kb.z, bb, a * n[6]); n[7] = fmaf(kb.w, bb, a * n[7]);
-      float num = (fmaf(S[4], qb.x, S[0] * qa.x) + fmaf(S[5], qb.y, S[1] * qa.y)) + (fmaf(S[6], qb.z, S[2] * qa.z) + fmaf(S[7], qb.w, S[3] * qa.w));
-      float nq = (fmaf(n[4], qb.x, n[0] * qa.x) + fmaf(n[5], qb.y, n[1] * qa.y)) + (fmaf(n[6], qb.z, n[2] * qa.z) + fmaf(n[7], qb.w, n[3] * qa.w));
+      const float fm = sf[b][tk] + m;
+      const float m_new = fmaxf(fm, si[b][tk]);
+      const float a = expf(fm - m_new), bb = expf(si[b][tk] - m_new);
+      const float4 v4 = *reinterpret_cast<const float4*>(&sv[b][tk][4 * cq]);
+      const float bv0 = bb * v4.x, bv1 = bb * v4.y, bv2 = bb * v4.z, bv3 = bb * v4.w;
+      const float4* k4 = reinterpret_cast<const float4*>(&sk[b][tk][rg * RQ]);
+      const float4* q4 = reinterpret_cast<const float4*>(&sq[b][tk][rg * RQ]);
+      float u0 = 0.f, u1 = 0.f, u2 = 0.f, u3 = 0.f, w = 0.f;
 #pragma unroll
-      for (int off = 1; off < LPC; off <<= 1) {
-        const float o1 = __shfl_xor_sync(0xffffffffu, num, off), o2 = __shfl_xor_sync(0xffffffffu, nq, off);
-        num += o1;
-        nq += o2;
+      for (int i = 0; i < RQ / 4; ++i) {
+        const float4 kk = k4[i], qq = q4[i];
+        const float kv[4] = {kk.x, kk.y, kk.z, kk.w}, qv[4] = {qq.x, qq.y, qq.z, qq.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int x = 4 * i + e;
+          S[0][x] = fmaf(kv[e], bv0, a * S[0][x]);
+          S[1][x] = fmaf(kv[e], bv1, a * S[1][x]);
+          S[2][x] = fmaf(kv[e], bv2, a * S[2][x]);
+          S[3][x] = fmaf(kv[e], bv3, a * S[3][x]);
+          n[x] = fmaf(kv[e], bb, a * n[x]);
+          u0 = fmaf(S[0][x], qv[e], u0);
+          u1 = fmaf(S[1][x], qv[e], u1);
+          u2 = fmaf(S[2][x], qv[e], u2);
+          u3 = fmaf(S[3][x], qv[e], u3);
+          w = fmaf(n[x], qv[e], w);
+        }
       }
       m = m_new;
-      if (q == 0) {
-        so[b][tk][col] = num;
-        sn[b][tk][col] = nq;
-        if (col == 0) sm[b][tk] = m_new;
+      *reinterpret_cast<float4*>(&pn[rg][tk][4 * cq]) = make_float4(u0, u1, u2, u3);
+      if (cq == 0) {
+        pq[rg][tk] = w;
+        if (rg == 0) sm[tk] = m_new;
       }
-      ka = ka2; kb = kb2; qa = qa2; qb = qb2;
-      ig = ig2; fg = fg2; vj = vj2;
     }
     mm_cp_async_wait_all();
     __syncthreads();
-    if (tid < nt * CB) {                         // (the next chunk's walk fills the other buffers; a barrier lies before these are written again)
-      const int tk = tid / CB, c = tid % CB;
-      if (blockIdx.x * CB + c < Dv)
+    for (int idx = tid; idx < nt * CB; idx += NT) {
+      const int tk = idx / CB, c = idx % CB;
+      if (blockIdx.x * CB + c < Dv) {
+        float num = 0.f, nq = 0.f;
+#pragma unroll
+        for (int g = 0; g < MM_RG; ++g) {
+          num += pn[g][tk][c];
+          nq += pq[g][tk];
+        }
         o[(size_t)(c0 + tk) * ldo + (size_t)h * Dv + blockIdx.x * CB + c] =
-            so[b][tk][c] * q_scale / (fmaxf(fabsf(sn[b][tk][c]) * q_scale, expf(-sm[b][tk])) + 1e-6f);
+            num * q_scale / (fmaxf(fabsf(nq) * q_scale, expf(-sm[tk])) + 1e-6f);
+      }
     }
+    __syncthreads();                             // (the parts are read: the next chunk's walk may write them)
   }
 #pragma unroll
   for (int i = 0; i < RQ; ++i) {
-    const int d = LPC * i + q;
-    if (d < D && j < Dv) Sg[(size_t)d * Dv + j] = S[i];
-    // column c of the block's first columns stores copy x0 + c (every column's n is the same)
-    if (col < CB / MM_COPY_COLS && x0 + col < X && d < D) ng[(size_t)(x0 + col) * D + d] = n[i];
+    const int d = rg * RQ + i;
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+      if (d < D && j0 + c < Dv) Sg[(size_t)d * Dv + j0 + c] = S[c][i];
+    // column quad c of the first quads stores copy x0 + c of the thread's rows (every column's n is the same)
+    if (cq < CB / MM_COPY_COLS && x0 + cq < X && d < D) ng[(size_t)(x0 + cq) * D + d] = n[i];
   }
-  if (q == 0 && col < CB / MM_COPY_COLS && x0 + col < X) mg[x0 + col] = m;
+  if (rg == 0 && cq < CB / MM_COPY_COLS && x0 + cq < X) mg[x0 + cq] = m;
 }
 
 constexpr int MM_MAX_D = 256;
@@ -181,13 +199,12 @@ FERRUM_API int ferrum_matrix_memory(const float* proj, int ldp, int off_q, int o
     matrix_memory_gates_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(proj, ldp, off_i, off_f, bias_i, bias_f, cap, n_tokens, H, gates);
     FERRUM_CHECK_LAUNCH("matrix_memory_gates");
   }
-#define MM_LAUNCH(LPC, TC)                                                                                                      \
-  matrix_memory_scan_kernel<LPC, TC><<<dim3((Dv + 256 / LPC - 1) / (256 / LPC), H, n_reqs), 256, 0, stream>>>(                  \
+#define MM_LAUNCH(RQ, TC)                                                                                                       \
+  matrix_memory_scan_kernel<RQ, TC><<<dim3((Dv + MM_CB - 1) / MM_CB, H, n_reqs), MM_THREADS, 0, stream>>>(                      \
       proj, ldp, off_q, off_k, off_v, gates, state, state_stride, q_start, slots, o, ldo, H, D, Dv)
-  if (D <= 32) MM_LAUNCH(4, 4);
-  else if (D <= 64) MM_LAUNCH(8, 8);
-  else if (D <= 128) MM_LAUNCH(16, 8);
-  else MM_LAUNCH(32, 4);
+  if (D <= 64) MM_LAUNCH(4, 8);
+  else if (D <= 128) MM_LAUNCH(8, 8);
+  else MM_LAUNCH(16, 4);
 #undef MM_LAUNCH
   FERRUM_CHECK_LAUNCH("matrix_memory_scan");
   return 0;

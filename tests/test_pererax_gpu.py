@@ -393,7 +393,7 @@ def test_routed_feed_forward_alone(cuda, dtype, E, F, Fs, n_exp, n_id, top, T):
     ffn.forward(x, ctx, y, accumulate=False)
     assert ctx.err.item() == 0
     sure = (margins[0] > (1e-6 if dtype == "float32" else CLEAR_CALL)).numpy()
-    assert sure.mean() > 0.5
+    assert sure.mean() >= 0.5
     got = y.double().cpu()
     assert (got - ref)[sure].abs().max() < (2e-4 if dtype == "float32" else 4e-2) * ref.abs().max()
     if n_id:            # the lifted identity output is in every token's choice: the result holds the token's own row

@@ -24,6 +24,10 @@ from .base import FeedForward, ParamSpec
 from .linear import RESIDUAL, STORE, STORE_F32, linear, linear_deferred, linear_swiglu
 
 
+# Up to this many tokens in a step a routed feed-forward's unit for every token runs on a second stream beside the routing.
+SIDE_STREAM_MAX_TOKENS = 64
+
+
 class SwiGLU(FeedForward):
     graph_safe = True
 
@@ -199,12 +203,31 @@ class RoutedFeedForward(FeedForward):
     def forward(self, x, ctx, residual, accumulate=True, defer=False):
         if accumulate:
             raise ValueError("a routed feed-forward hands its result to a block that adds it")
-        add = None
+        add = join = None
         if self.shared is not None:
             add = ctx.buf("moe_shared", (ctx.token_capacity, self.width), torch.float32)
-            self.shared.forward(x, ctx, add, accumulate=False)
-            ctx.flush_residual()
+            if ctx.n_tokens <= SIDE_STREAM_MAX_TOKENS and not ops.profiling() and str(ctx.device) != "cpu":
+                # The unit for every token and the routed experts meet only in the sum.  In steps of a few tokens every
+                # kernel of a chain waits for the one before it far longer than it computes: the unit runs on a second
+                # stream beside the routing (its products use the second lane's workspace).
+                ctx.flush_residual()
+                side, fork, join = ctx.side_stream()
+                fork.record(torch.cuda.current_stream())
+                side.wait_event(fork)
+                ctx.lane = 1
+                try:
+                    with torch.cuda.stream(side):
+                        self.shared.forward(x, ctx, add, accumulate=False)
+                        ctx.flush_residual()
+                        join.record(side)
+                finally:
+                    ctx.lane = 0
+            else:
+                self.shared.forward(x, ctx, add, accumulate=False)
+                ctx.flush_residual()
         rows, row_of, top = self.forward_rows(x, ctx)
+        if join is not None:
+            torch.cuda.current_stream().wait_event(join)
         ops.moe_combine(rows, row_of, top, ctx.n_tokens, residual, weight_of=None if self.scale_input else self._weight_of,
                         x=x if self.identity else None, add=add)
         return None

@@ -15,6 +15,10 @@ from ..ops import lib as ops
 from .base import CacheNeed, Mixer, ParamSpec
 
 
+# Up to this many tokens in a step the right mixer runs on a second stream beside the left one.
+SIDE_STREAM_MAX_TOKENS = 64
+
+
 class ParallelMixer(Mixer):
     graph_safe = True
 
@@ -46,9 +50,30 @@ class ParallelMixer(Mixer):
         cap, E = ctx.token_capacity, self.width
         ya = ctx.buf("pair_left", (cap, E), torch.float32)
         yb = ctx.buf("pair_right", (cap, E), torch.float32)
-        self.left.forward(x, ctx, cache, ya, accumulate=False)
-        ctx.flush_residual()
-        self.right.forward(x, ctx, cache, yb, accumulate=False)
-        ctx.flush_residual()
+        if ctx.n_tokens <= SIDE_STREAM_MAX_TOKENS and not ops.profiling() and str(ctx.device) != "cpu":
+            # The two meet only in the sum.  In steps of a few tokens every kernel of a chain waits for the one before it far
+            # longer than it computes: the right mixer runs on a second stream beside the left one (its products use the
+            # second lane's workspace; the two keep different things of the cache and use scratch buffers of their own).
+            ctx.flush_residual()
+            side, fork, join = ctx.side_stream()
+            main = torch.cuda.current_stream()
+            fork.record(main)
+            side.wait_event(fork)
+            ctx.lane = 1
+            try:
+                with torch.cuda.stream(side):
+                    self.right.forward(x, ctx, cache, yb, accumulate=False)
+                    ctx.flush_residual()
+                    join.record(side)
+            finally:
+                ctx.lane = 0
+            self.left.forward(x, ctx, cache, ya, accumulate=False)
+            ctx.flush_residual()
+            main.wait_event(join)
+        else:
+            self.left.forward(x, ctx, cache, ya, accumulate=False)
+            ctx.flush_residual()
+            self.right.forward(x, ctx, cache, yb, accumulate=False)
+            ctx.flush_residual()
         ops.dual_norm_mean(ya, yb, self.w_left_out, self.w_right_out, self.eps, residual, ctx.n_tokens)
         return None

@@ -19,9 +19,9 @@
 //                      S <- dec * S (row d by dec[d]);  e = beta * (v - S^T k);  S <- S + k e^T;  o = S^T q
 //                    (o is formed as S^T q of the decayed S plus e (k . q), so that both sums over the rows and k . q
 //                    cross the lanes side by side)
-//                    with beta = sigmoid(its logit).  D / 8 lanes share a column (eight rows each; a lane adds its rows
-//                    into four sums that it folds pairwise) and add their parts by shuffles: one fixed tree, token by
-//                    token whatever the portion, so a token's result does not depend on how the sequence was cut.
+//                    with beta = sigmoid(its logit).  Four lanes share a column (a quarter of the rows each, summed in
+//                    row order) and add their parts by two shuffles: one fixed tree, token by token whatever the
+//                    portion, so a token's result does not depend on how the sequence was cut.
 #include "common.cuh"
 
 constexpr int DR_MAX_TAPS = 16;
@@ -109,7 +109,158 @@ __device__ __forceinline__ void dr_cp_async4(float* smem, const float* gmem) {
 __device__ __forceinline__ void dr_cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void dr_cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
-// LPC lanes share a value column (D <= 8 LPC): lane q of them holds rows d = LPC i + q, i < 8, of the column in registers,
+__device__ __forceinline__ void dr_cp_async16(float* smem, const float* gmem) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(a), "l"(gmem) : "memory");
+}
+
+// The walk for steps of single tokens (a few tokens a request).  Four lanes share a value column: lane q of them holds the rows d = q RQ .. q RQ + RQ - 1 (D <= 4 RQ) of C neighbouring
+// columns in registers, and a block of 64 threads walks 16 C columns.  What bounds such a walk is the path between shared
+// memory and the registers, which a 16-byte read and a shuffle each occupy for four cycles per warp: so a lane keeps many
+// rows (two shuffle levels per sum instead of four), every k, q and decay it reads serves its C columns, and k stays in
+// registers between the two halves of a token's step.  TC tokens are staged at a time (a quarter's rows 16 bytes apart from
+// the next quarter's, so that the quarters' reads fall into different banks), the next chunk on its way meanwhile by
+// cp.async straight to its place (16 bytes a copy where the rows allow; loads into registers that were still pending held
+// up the walk's own shared-memory reads); a chunk's read-outs leave together after its walk.  Its reads and writes of the
+// state are whole 64-byte pieces of a row per warp, which is what a step of single tokens consists of; over a prompt its one
+// or two warps a block run a token's long rows slower than the kernel below (measured: 1,030 against 600 us for 2,048 tokens).
+template <int RQ, int C, int TC>
+__global__ void __launch_bounds__(64)
+delta_scan_rows_kernel(const float* __restrict__ qkv, int Cw, const float* __restrict__ dec, float* __restrict__ state,
+                  long long state_stride, const int* __restrict__ q_start, const int* __restrict__ slots, float* __restrict__ o,
+                  int ldo, int H, int G, int D, int Dv, int vec) {
+  constexpr int NT = 64, QS = RQ + 4, W = 4 * QS, WD = 4 * RQ, CB = (NT / 4) * C;
+  static_assert(RQ % 4 == 0 && TC <= NT, "rows are read four at a time");
+  __shared__ __align__(16) float sq[2][TC][W], sk[2][TC][W], sg[2][TC][W];
+  __shared__ float sv[2][TC][CB], sb[2][TC], so[2][TC][CB];
+  const int tid = threadIdx.x, q = tid & 3, cp = tid >> 2;
+  const int jb = blockIdx.x * CB, j0 = jb + cp * C, h = blockIdx.y, r = blockIdx.z;
+  const int g = h / (H / G);
+  const int t0 = q_start[r], t1 = q_start[r + 1];
+  const int ldd = H * D + H;
+  float* Sg = state + (long long)slots[r] * state_stride + (size_t)h * D * Dv;
+  const int off_q = g * D, off_k = G * D + g * D, off_v = 2 * G * D + h * Dv + jb;
+  auto stage = [&](int c0, int b) {              // a chunk's elements on their way into buffer b
+    const int nt = min(TC, t1 - c0);
+    if (vec) {                                   // rows of whole 16-byte groups: a copy brings four rows
+      for (int idx = tid; idx < TC * 3 * (WD / 4); idx += NT) {
+        const int which = idx / (TC * (WD / 4)), tk = (idx / (WD / 4)) % TC, d = (idx % (WD / 4)) * 4;
+        float* dst = (which == 0 ? &sq[b][tk][0] : (which == 1 ? &sk[b][tk][0] : &sg[b][tk][0])) + (d / RQ) * QS + d % RQ;
+        if (tk < nt && d < D) {
+          const size_t row = (size_t)(c0 + tk);
+          dr_cp_async16(dst, which == 0 ? qkv + row * Cw + off_q + d : (which == 1 ? qkv + row * Cw + off_k + d : dec + row * ldd + (size_t)h * D + d));
+        } else {
+          const float fill = which == 2 ? 1.f : 0.f;
+          *reinterpret_cast<float4*>(dst) = make_float4(fill, fill, fill, fill);
+        }
+      }
+    } else {
+      for (int idx = tid; idx < TC * 3 * WD; idx += NT) {
+        const int which = idx / (TC * WD), tk = (idx / WD) % TC, d = idx % WD;
+        float* dst = (which == 0 ? &sq[b][tk][0] : (which == 1 ? &sk[b][tk][0] : &sg[b][tk][0])) + (d / RQ) * QS + d % RQ;
+        if (tk < nt && d < D) {
+          const size_t row = (size_t)(c0 + tk);
+          dr_cp_async4(dst, which == 0 ? qkv + row * Cw + off_q + d : (which == 1 ? qkv + row * Cw + off_k + d : dec + row * ldd + (size_t)h * D + d));
+        } else {
+          *dst = which == 2 ? 1.f : 0.f;
+        }
+      }
+    }
+    for (int idx = tid; idx < TC * CB; idx += NT) {
+      const int tk = idx / CB, c = idx % CB;
+      if (tk < nt && jb + c < Dv) dr_cp_async4(&sv[b][tk][c], qkv + (size_t)(c0 + tk) * Cw + off_v + c);
+      else sv[b][tk][c] = 0.f;
+    }
+    if (tid < nt) dr_cp_async4(&sb[b][tid], dec + (size_t)(c0 + tid) * ldd + H * D + h);
+    dr_cp_async_commit();
+  };
+  if (t0 < t1) stage(t0, 0);
+  float S[C][RQ];
+#pragma unroll
+  for (int i = 0; i < RQ; ++i) {
+    const int d = q * RQ + i;
+#pragma unroll
+    for (int c = 0; c < C; ++c) S[c][i] = (d < D && j0 + c < Dv) ? Sg[(size_t)d * Dv + j0 + c] : 0.f;
+  }
+  dr_cp_async_wait_all();
+  __syncthreads();
+  int b = 0;
+  for (int c0 = t0; c0 < t1; c0 += TC, b ^= 1) {
+    const int nt = min(TC, t1 - c0);
+    if (c0 + TC < t1) stage(c0 + TC, b ^ 1);     // (that buffer was last read before the barrier that ended the chunk before)
+    for (int tk = 0; tk < nt; ++tk) {
+      const float4* g4 = reinterpret_cast<const float4*>(&sg[b][tk][q * QS]);
+      const float4* k4 = reinterpret_cast<const float4*>(&sk[b][tk][q * QS]);
+      const float4* q4 = reinterpret_cast<const float4*>(&sq[b][tk][q * QS]);
+      const float beta = sb[b][tk];
+      float vj[C], part[C], po[C], kq = 0.f, kr[RQ];
+#pragma unroll
+      for (int c = 0; c < C; ++c) {
+        vj[c] = sv[b][tk][cp * C + c];
+        part[c] = 0.f;
+        po[c] = 0.f;
+      }
+      // The read-out sees the token's write: (S + k e^T)^T q = S^T q + e (k . q).  So S^T k, S^T q (both of the decayed S)
+      // and k . q are summed across the lanes side by side, and one chain of shuffles serves the token.
+#pragma unroll
+      for (int i = 0; i < RQ / 4; ++i) {
+        const float4 gg = g4[i], kk = k4[i], qq = q4[i];
+        const float gv[4] = {gg.x, gg.y, gg.z, gg.w}, kv[4] = {kk.x, kk.y, kk.z, kk.w}, qv[4] = {qq.x, qq.y, qq.z, qq.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int x = 4 * i + e;
+          kr[x] = kv[e];
+          kq = fmaf(kv[e], qv[e], kq);
+#pragma unroll
+          for (int c = 0; c < C; ++c) {
+            S[c][x] *= gv[e];
+            part[c] = fmaf(S[c][x], kv[e], part[c]);
+            po[c] = fmaf(S[c][x], qv[e], po[c]);
+          }
+        }
+      }
+#pragma unroll
+      for (int off = 1; off < 4; off <<= 1) {
+        float t1v[C], t2v[C];
+#pragma unroll
+        for (int c = 0; c < C; ++c) {
+          t1v[c] = __shfl_xor_sync(0xffffffffu, part[c], off);
+          t2v[c] = __shfl_xor_sync(0xffffffffu, po[c], off);
+        }
+        const float t3 = __shfl_xor_sync(0xffffffffu, kq, off);
+#pragma unroll
+        for (int c = 0; c < C; ++c) {
+          part[c] += t1v[c];
+          po[c] += t2v[c];
+        }
+        kq += t3;
+      }
+#pragma unroll
+      for (int c = 0; c < C; ++c) {
+        const float e = beta * (vj[c] - part[c]);
+        po[c] = fmaf(e, kq, po[c]);
+#pragma unroll
+        for (int x = 0; x < RQ; ++x) S[c][x] = fmaf(kr[x], e, S[c][x]);
+        if (q == 0) so[b][tk][cp * C + c] = po[c];
+      }
+    }
+    dr_cp_async_wait_all();
+    __syncthreads();
+    for (int idx = tid; idx < nt * CB; idx += NT) {      // (the next chunk's walk fills the other buffer; a barrier lies before this one is written again)
+      const int tk = idx / CB, c = idx % CB;
+      if (jb + c < Dv) o[(size_t)(c0 + tk) * ldo + (size_t)h * Dv + jb + c] = so[b][tk][c];
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < RQ; ++i) {
+    const int d = q * RQ + i;
+#pragma unroll
+    for (int c = 0; c < C; ++c)
+      if (d < D && j0 + c < Dv) Sg[(size_t)d * Dv + j0 + c] = S[c][i];
+  }
+}
+
+// The walk for portions of many tokens.  LPC lanes share a value column (D <= 8 LPC): lane q of them holds rows d = LPC i + q, i < 8, of the column in registers,
 // and a block of 256 threads walks 256 / LPC columns.  TC tokens are staged at a time; a staged token row keeps the lanes'
 // elements apart (lane q at 12 q + i, so that a lane reads its rows four at a time and the lanes' 16-byte reads spread over
 // the banks).  The chunk after the one being walked is on its way meanwhile, element by element with cp.async straight to
@@ -117,7 +268,7 @@ __device__ __forceinline__ void dr_cp_async_wait_all() { asm volatile("cp.async.
 // token's operands are read one token ahead of their use.
 template <int LPC, int TC>
 __global__ void __launch_bounds__(256)
-delta_scan_kernel(const float* __restrict__ qkv, int C, const float* __restrict__ dec, float* __restrict__ state,
+delta_scan_lanes_kernel(const float* __restrict__ qkv, int C, const float* __restrict__ dec, float* __restrict__ state,
                   long long state_stride, const int* __restrict__ q_start, const int* __restrict__ slots, float* __restrict__ o,
                   int ldo, int H, int G, int D, int Dv) {
   constexpr int RQ = 8, QS = RQ + 4, W = LPC * QS, WD = LPC * RQ, CB = 256 / LPC;
@@ -217,6 +368,7 @@ delta_scan_kernel(const float* __restrict__ qkv, int C, const float* __restrict_
 }
 
 constexpr int DR_MAX_D = 256;
+constexpr int DR_ROWS_MAX_TOKENS = 4;     // the longest portion of a step that still takes the single-token walk
 
 // proj: float32 rows [q | k | v | beta logits] of stride ldp; logit: float32 rows [H * D] of stride ldl (the decays' logits);
 // conv_w: [C][taps]; state: [slots][state_stride] float32 rows, S first and the convolution's inputs from H * D * Dv on;
@@ -224,7 +376,7 @@ constexpr int DR_MAX_D = 256;
 FERRUM_API int ferrum_delta_rule(const float* proj, int ldp, const float* logit, int ldl, int n_tokens, int n_reqs,
                                  const int* req_of_token, const int* q_start, const int* slots, const float* conv_w, int taps,
                                  const float* dt_bias, const float* a_log, int H, int G, int D, int Dv, float* state,
-                                 long long state_stride, float* qkv, float* dec, float* o, int ldo, cudaStream_t stream) {
+                                 long long state_stride, float* qkv, float* dec, float* o, int ldo, int max_q_len, cudaStream_t stream) {
   FERRUM_CHECK_ARG(H > 0 && G > 0 && H % G == 0 && D > 0 && D <= DR_MAX_D && Dv > 0, "delta_rule: bad head sizes H=%d G=%d D=%d Dv=%d", H, G, D, Dv);
   FERRUM_CHECK_ARG(taps >= 1 && taps <= DR_MAX_TAPS, "delta_rule: %d convolution taps are outside 1..%d", taps, DR_MAX_TAPS);
   const int C = 2 * G * D + H * Dv;
@@ -246,13 +398,29 @@ FERRUM_API int ferrum_delta_rule(const float* proj, int ldp, const float* logit,
                                                                              slots, n_reqs);
     FERRUM_CHECK_LAUNCH("delta_conv_state");
   }
-#define DR_LAUNCH(LPC, TC)                                                                                                     \
-  delta_scan_kernel<LPC, TC><<<dim3((Dv + 256 / LPC - 1) / (256 / LPC), H, n_reqs), 256, 0, stream>>>(                        \
+  if (max_q_len > DR_ROWS_MAX_TOKENS) {
+#define DR_LAUNCH_LANES(LPC, TC)                                                                                               \
+  delta_scan_lanes_kernel<LPC, TC><<<dim3((Dv + 256 / LPC - 1) / (256 / LPC), H, n_reqs), 256, 0, stream>>>(                  \
       qkv, C, dec, state, state_stride, q_start, slots, o, ldo, H, G, D, Dv)
-  if (D <= 32) DR_LAUNCH(4, 4);
-  else if (D <= 64) DR_LAUNCH(8, 8);
-  else if (D <= 128) DR_LAUNCH(16, 8);
-  else DR_LAUNCH(32, 4);
+    if (D <= 32) DR_LAUNCH_LANES(4, 4);
+    else if (D <= 64) DR_LAUNCH_LANES(8, 8);
+    else if (D <= 128) DR_LAUNCH_LANES(16, 8);
+    else DR_LAUNCH_LANES(32, 4);
+#undef DR_LAUNCH_LANES
+    FERRUM_CHECK_LAUNCH("delta_scan");
+    return 0;
+  }
+  // whole 16-byte groups of rows in every staged array, on 16-byte borders
+  const int vec = D % 4 == 0 && C % 4 == 0 && (H * D + H) % 4 == 0 && (G * D) % 4 == 0 && ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)dec & 15) == 0;
+  // one column a thread while that still leaves blocks for every SM to spare (a prompt of one request), else two
+  const bool wide = (long long)((Dv + 15) / 16) * H * n_reqs > 160;
+#define DR_LAUNCH(RQ, CC, TC)                                                                                                  \
+  delta_scan_rows_kernel<RQ, CC, TC><<<dim3((Dv + 16 * CC - 1) / (16 * CC), H, n_reqs), 64, 0, stream>>>(                           \
+      qkv, C, dec, state, state_stride, q_start, slots, o, ldo, H, G, D, Dv, vec)
+  if (D <= 32) { if (wide) DR_LAUNCH(8, 2, 16); else DR_LAUNCH(8, 1, 16); }
+  else if (D <= 64) { if (wide) DR_LAUNCH(16, 2, 16); else DR_LAUNCH(16, 1, 16); }
+  else if (D <= 128) { if (wide) DR_LAUNCH(32, 2, 8); else DR_LAUNCH(32, 1, 8); }
+  else DR_LAUNCH(64, 1, 4);
 #undef DR_LAUNCH
   FERRUM_CHECK_LAUNCH("delta_scan");
   return 0;

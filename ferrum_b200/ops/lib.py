@@ -1139,7 +1139,7 @@ def delta_rule(proj, logit, n_tokens, ctx, conv_w, dt_bias, a_log, H, G, D, Dv, 
     _check(lib().ferrum_delta_rule(_ptr(proj), c_int(proj.stride(0)), _ptr(logit), c_int(logit.stride(0)), c_int(n_tokens),
                                    c_int(ctx.n_reqs), _ptr(ctx.req_of_token), _ptr(ctx.q_start), _ptr(ctx.slots), _ptr(conv_w),
                                    c_int(taps), _ptr(dt_bias), _ptr(a_log), c_int(H), c_int(G), c_int(D), c_int(Dv), _ptr(state),
-                                   c_longlong(state.stride(0)), _ptr(qkv), _ptr(dec), _ptr(o), c_int(o.stride(0)), _stream()),
+                                   c_longlong(state.stride(0)), _ptr(qkv), _ptr(dec), _ptr(o), c_int(o.stride(0)), c_int(ctx.max_q_len), _stream()),
            "delta_rule")
     launches += 2 if taps > 1 else 1       # (the entry point launches the preparation, the convolution's state and the walk)
 

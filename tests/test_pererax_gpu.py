@@ -378,7 +378,8 @@ def test_routed_feed_forward_alone(cuda, dtype, E, F, Fs, n_exp, n_id, top, T):
     ffn = RoutedFeedForward(E, F, n_exp, top, td, act="swish_clamp", scores="softmax", scale_input=False, correction=True,
                             weight_scale=1.7, identity=n_id, limit=1.2, shared=shared)
     # a correction that lifts the first identity output into every token's choice (and changes no weight)
-    fixed = {"correction": torch.cat([0.1 * torch.randn(n_exp + n_id - 1), torch.tensor([5.0])])} if n_id else None
+    drawn = 0.1 * torch.randn(n_exp + n_id - 1, generator=torch.Generator().manual_seed(23))
+    fixed = {"correction": torch.cat([drawn, torch.tensor([5.0])])} if n_id else None
     w = fill_part(ffn, 21, td, "f.", std=0.4, fixed=fixed)
     g = torch.Generator(device="cuda").manual_seed(22)
     x = torch.randn(T, E, device="cuda", generator=g).to(td)
@@ -393,7 +394,7 @@ def test_routed_feed_forward_alone(cuda, dtype, E, F, Fs, n_exp, n_id, top, T):
     ffn.forward(x, ctx, y, accumulate=False)
     assert ctx.err.item() == 0
     sure = (margins[0] > (1e-6 if dtype == "float32" else CLEAR_CALL)).numpy()
-    assert sure.mean() >= 0.5
+    assert sure.any() and sure.mean() >= min(0.5, 1.0 - 1.0 / T)
     got = y.double().cpu()
     assert (got - ref)[sure].abs().max() < (2e-4 if dtype == "float32" else 4e-2) * ref.abs().max()
     if n_id:            # the lifted identity output is in every token's choice: the result holds the token's own row

@@ -11,6 +11,7 @@ peaks.  This is the small case that `ncu` captures are taken on.
     python kernel_bench.py head_linear --tokens 8 --hq 16 --n 512 --k 128
     python kernel_bench.py attn_decode|attn_prefill --exact [--window W] [--penalty]   (float32 weights and sums on 16-bit storage)
     python kernel_bench.py ssm --tokens 2048 [--batch 1] [--hq 64] [--head-dim 64] [--state 128]   (the state-space mixer's kernels)
+    python kernel_bench.py delta|memory --tokens 2048 [--batch 1] [--hq 16] [--head-dim 128]   (the walks of the gated delta rule and of the matrix memory)
     python kernel_bench.py moe --tokens 4096 --n 2816 --k 2048 [--experts 8] [--epilogue store|swiglu] [--mma-sync] [--cuda-cores]   (grouped product of a routed feed-forward)
     python kernel_bench.py streams --tokens 2048 --k 2048 [--streams 4]   (write, read and norm over the residual streams)
     python kernel_bench.py rmsnorm|rope --tokens 8

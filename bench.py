@@ -609,8 +609,8 @@ def delta_configs(size, layers, vocab=32000, window=1024):
     delta = {"heads": s["memory_heads"], "kv_heads": s["memory_heads"], "dim": s["dim"], "vdim": s["vdim"], "conv": 4,
              "decay_rank": s["rank"], "gate_rank": s["rank"]}
     mlp = {"kind": "moe", "expert": {"ff": s["expert_ff"], "limit": 7.0}, "shared": {"ff": s["shared_ff"], "limit": 7.0},
-           "router": {"experts": s["experts"], "identity": s["identity"], "top": s["top"], "scale": 2.0}}
-    kinds = [{"type": "parallel", "mixer": {"left": dict(att, softcap=30.0), "right": memory}},
+           "router": {"experts": s["experts"], "identity": s["identity"], "top": s["top"], "scale": 2.5}}
+    kinds = [{"type": "parallel", "mixer": {"left": dict(att, softcap=50.0), "right": memory}},
              {"type": "attention", "mixer": dict(att, mask={"size": window})},
              {"type": "channel_delta", "mixer": delta}, {"type": "channel_delta", "mixer": delta}]
     ours = {"architecture": "Pererax", "vocab": vocab, "width": s["width"], "norm": {"eps": 1e-6},

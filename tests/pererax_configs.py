@@ -6,8 +6,8 @@ a delta mixer with fewer query/key heads than value heads, three taps and two di
 of its low-rank pairs; a layer without feed-forward; two layers that run another layer's tensors; a
 window that is no multiple of a page.
 B: everything a multiple of 8, so that 16-bit runs take the tensor-core products; as many KV heads as
-query heads in one attention and one KV head in the other; a window longer than two pages; four of
-eight experts plus two identity outputs; key size 64 in the recurrences.
+query heads in one attention and one KV head in the other; a window longer than two pages; three of
+six experts plus three identity outputs; key size 64 in the recurrences.
 C: the smallest of everything: one head, a window of one key, one tap, one expert chosen out of one
 plus one identity output, no unit for every token, no soft cap, no rotation on the left of the pair,
 a scale of one on the router's weights.
@@ -30,19 +30,19 @@ PERERAX_A = {
         {"type": "channel_delta", "mixer": _DELTA_A, "mlp": _MLP_A, "weights_of": 2},
     ],
 }
-_MLP_B = {"kind": "moe", "expert": {"ff": 64, "limit": 2.0}, "router": {"experts": 8, "identity": 2, "top": 4, "scale": 2.0},
-          "shared": {"ff": 96, "limit": 1.0}}
+_MLP_B = {"kind": "moe", "expert": {"ff": 64, "limit": 1.75}, "router": {"experts": 6, "identity": 3, "top": 3, "scale": 1.25},
+          "shared": {"ff": 96, "limit": 0.9}}
 PERERAX_B = {
     "architecture": "Pererax", "vocab": 256, "width": 128, "norm": {"eps": 3e-6},
     "layers": [
         {"type": "channel_delta", "mixer": {"heads": 4, "kv_heads": 4, "dim": 64, "vdim": 32, "conv": 4, "decay_rank": 16, "gate_rank": 8},
          "mlp": _MLP_B},
-        {"type": "attention", "mixer": {"heads": 4, "kv_heads": 4, "dim": 32, "vdim": 32, "scale": 0.2, "mask": {"size": 40},
+        {"type": "attention", "mixer": {"heads": 4, "kv_heads": 4, "dim": 32, "vdim": 32, "scale": 0.2, "mask": {"size": 36},
                                         "rot": {"base": 10000.0, "dims": 32}}, "mlp": _MLP_B},
         {"type": "parallel", "mixer": {"left": {"heads": 4, "kv_heads": 1, "dim": 32, "vdim": 32, "scale": 0.18, "softcap": 20.0,
                                                 "rot": {"base": 20000.0, "dims": 16}},
-                                       "right": {"heads": 2, "dim": 64, "vdim": 40, "gate_cap": 12.0}}, "mlp": _MLP_B},
-        {"type": "attention", "mixer": {"heads": 4, "kv_heads": 4, "dim": 32, "vdim": 32, "scale": 0.2, "mask": {"size": 40},
+                                       "right": {"heads": 2, "dim": 64, "vdim": 40, "gate_cap": 10.0}}, "mlp": _MLP_B},
+        {"type": "attention", "mixer": {"heads": 4, "kv_heads": 4, "dim": 32, "vdim": 32, "scale": 0.2, "mask": {"size": 36},
                                         "rot": {"base": 10000.0, "dims": 32}}, "mlp": _MLP_B, "weights_of": 1},
     ],
 }

@@ -177,7 +177,7 @@ def attention_reference(q, k, v, pos, H, G, scale, size, cap, sink):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H,G,D,page,size,cap,sink", [(3, 1, 14, 8, 19, 0.0, False), (8, 1, 64, 16, 0, 30.0, True), (4, 2, 64, 16, 40, 0.0, False),
+@pytest.mark.parametrize("H,G,D,page,size,cap,sink", [(3, 1, 14, 8, 19, 0.0, False), (8, 2, 64, 16, 0, 25.0, True), (6, 3, 64, 16, 44, 0.0, False),
                                                       (6, 2, 80, 16, 130, 4.0, True), (5, 5, 40, 32, 257, 0.0, True), (2, 1, 200, 8, 0, 2.5, False),
                                                       (1, 1, 32, 16, 1, 0.0, True)])
 def test_attention_kernel_with_sink_cap_and_window_edges(cuda, dtype, H, G, D, page, size, cap, sink):
@@ -286,7 +286,7 @@ def inputs(n, E, td, seed=10, count=1):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H,G,D,Dv,size,R,cap", [(3, 1, 10, 14, 0, 6, 3.0), (8, 1, 64, 64, 0, 64, 30.0), (4, 2, 64, 64, 40, 64, 0.0), (4, 2, 12, 12, 17, 8, 0.0),
+@pytest.mark.parametrize("H,G,D,Dv,size,R,cap", [(3, 1, 10, 14, 0, 6, 3.0), (8, 2, 64, 64, 0, 32, 25.0), (6, 3, 64, 64, 44, 64, 0.0), (4, 2, 12, 12, 17, 8, 0.0),
                                                  (2, 2, 6, 6, 1, 0, 0.0), (6, 2, 80, 40, 24, 20, 5.0)])
 def test_both_attention_mixers_alone(cuda, dtype, H, G, D, Dv, size, R, cap):
     """Attention with the norm over the whole query and key projections and a rotation of part of each head: with
@@ -314,7 +314,7 @@ def test_both_attention_mixers_alone(cuda, dtype, H, G, D, Dv, size, R, cap):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H,D,Dv,cap", [(3, 6, 10, 7.0), (4, 48, 48, 12.0), (2, 64, 40, 12.0), (1, 5, 33, 4.0), (2, 130, 70, 3.0), (1, 200, 8, 9.0)])
+@pytest.mark.parametrize("H,D,Dv,cap", [(3, 6, 10, 7.0), (3, 40, 56, 10.0), (2, 64, 40, 14.0), (1, 5, 33, 4.0), (2, 130, 70, 3.0), (1, 200, 8, 9.0)])
 def test_matrix_memory_mixer_alone(cuda, dtype, H, D, Dv, cap):
     """The matrix-memory recurrence: whole, in portions and token pairs (state rows carried between steps, a
     running maximum that starts at zero), at key sizes that take each of the walk's register layouts."""
@@ -331,7 +331,7 @@ def test_matrix_memory_mixer_alone(cuda, dtype, H, D, Dv, cap):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H,G,D,Dv,taps,ra,rg", [(4, 2, 10, 6, 3, 5, 7), (4, 4, 32, 64, 4, 24, 24), (2, 1, 64, 40, 4, 16, 8), (1, 1, 4, 36, 1, 1, 2),
+@pytest.mark.parametrize("H,G,D,Dv,taps,ra,rg", [(4, 2, 10, 6, 3, 5, 7), (6, 6, 32, 48, 4, 12, 20), (2, 1, 64, 40, 4, 16, 8), (1, 1, 4, 36, 1, 1, 2),
                                                  (2, 2, 130, 33, 2, 9, 3), (3, 1, 200, 8, 5, 8, 16)])
 def test_delta_rule_mixer_alone(cuda, dtype, H, G, D, Dv, taps, ra, rg):
     """The gated delta rule behind its short convolutions: whole, in portions shorter than the taps and token pairs
@@ -366,8 +366,8 @@ def test_pair_of_mixers_alone(cuda, dtype):
 
 # ================================================================= the feed-forward and the norms alone
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("E,F,Fs,n_exp,n_id,top,T", [(52, 20, 28, 5, 2, 3, 37), (128, 64, 96, 8, 2, 4, 300), (40, 24, 0, 1, 1, 1, 9), (64, 32, 16, 16, 0, 4, 70),
-                                                     (72, 100, 8, 3, 0, 3, 11), (128, 128, 256, 4, 3, 2, 1000), (256, 96, 128, 8, 2, 4, 2)])
+@pytest.mark.parametrize("E,F,Fs,n_exp,n_id,top,T", [(52, 20, 28, 5, 2, 3, 37), (128, 64, 96, 6, 3, 3, 300), (40, 24, 0, 1, 1, 1, 9), (64, 32, 16, 16, 0, 4, 70),
+                                                     (72, 100, 8, 3, 0, 3, 11), (128, 128, 256, 4, 3, 2, 1000), (256, 80, 160, 6, 1, 3, 2)])
 def test_routed_feed_forward_alone(cuda, dtype, E, F, Fs, n_exp, n_id, top, T):
     """Clamped units chosen by softmax scores plus a correction, identity experts, a unit for every token: sizes that
     take each of the product kernels (CUDA cores, a few rows an expert, tensor-core tiles of both kinds)."""
